@@ -3,7 +3,8 @@
 Run-order entries (caches) whose mixers have the same needs as to which keys
 must stay (all of them, or a window) form a group; a group has one pool of page
 ids and one block table per request, and each cache of the group has its own
-tensor [pages, 2, kv_heads, page_size, head_dim] indexed by those ids.  The
+tensor [pages, planes, kv_heads, page_size, head_dim] indexed by those ids
+(two planes for keys and values, one for a mixer that caches a single row per token).  The
 reference keeps one tensor [layers, pages, 2, page_size, kv_heads, head_dim] per
 model component (mstar/engine/kv_cache_engine.py:132-136); here a page keeps the
 tokens of one head contiguous, so a page of one head is one 16-byte-aligned run
@@ -59,7 +60,7 @@ def bytes_per_page(needs: Sequence[CacheNeed], group_of, group: int, page_size: 
     total = 0
     for need, g in zip(needs, group_of):
         if g == group:
-            total += 2 * need.kv.num_kv_heads * page_size * need.kv.head_dim * item
+            total += need.kv.planes * need.kv.num_kv_heads * page_size * need.kv.head_dim * item
     return total
 
 
@@ -92,7 +93,7 @@ class CacheStorage:
                 # fixed-shape (CUDA graph) batches write their keys there
                 n = self.group_configs[g].num_pages + 1
                 self.kv.append(torch.zeros(
-                    (n, 2, need.kv.num_kv_heads, self.page_sizes[g], need.kv.head_dim),
+                    (n, need.kv.planes, need.kv.num_kv_heads, self.page_sizes[g], need.kv.head_dim),
                     dtype=dtype, device=device))
             if need is not None and need.state is not None:
                 self.state.append(torch.zeros((self.num_slots + 1,) + tuple(need.state.shape),

@@ -91,6 +91,80 @@ class GatedMLPSpec:
 
 
 @dataclass(frozen=True)
+class MatrixMemorySpec:
+    """kind "mlstm": a matrix memory per head (the mLSTM cell of xLSTM), carried from token
+    to token as per-request state instead of a key/value cache.
+
+    Per head, with q scaled by ``dim ** -0.5``, log input gate i and log forget gate f
+    (both soft-capped at ``gate_cap``, f through logsigmoid), and a running maximum m that
+    starts at 0:  m' = max(f + m, i);  S' = exp(f + m - m') S + exp(i - m') k v^T;  n'
+    likewise with k;  out = S'^T q / (max(|n' . q|, exp(-m')) + ``denom_floor``).  Each
+    head's output is divided by its root mean square (``norm_eps``), scaled by a weight,
+    gated by sigmoid(W_g x) and projected back.
+    """
+
+    kind: str = "mlstm"
+    hidden_size: int = 0
+    num_heads: int = 0
+    qk_dim: int = 0
+    v_dim: int = 0
+    gate_cap: float = 15.0
+    norm_eps: float = 1e-6
+    denom_floor: float = 1e-6
+    shares_kv: bool = False
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """kind "latent_attention": softmax attention whose keys and values are up-projections
+    of one cached latent vector per token.
+
+    A token caches ``kv_rank`` latent features (RMS-normed, plain weight) and ``rot_dim``
+    rotated key features shared by all heads.  Head h scores a key as
+    ``(q_plain . W_uk[h] c + q_rot . k_rot) * scale`` and reads the value ``W_uv[h] c``.
+    ``position`` rotates the ``rot_dim`` part of queries and of the shared key.
+    ``window``: None keeps every key; W lets position p see p-W+1 .. p.  ``gated``:
+    the concatenated heads are multiplied by sigmoid(W_g x) before the output product.
+    """
+
+    kind: str = "latent_attention"
+    hidden_size: int = 0
+    num_heads: int = 0
+    qk_dim: int = 0
+    rot_dim: int = 0
+    v_dim: int = 0
+    kv_rank: int = 0
+    position: PositionSpec = field(default_factory=PositionSpec)
+    window: Optional[int] = None
+    scale: Optional[float] = None
+    norm_eps: float = 1e-6
+    gated: bool = True
+    shares_kv: bool = False
+
+
+@dataclass(frozen=True)
+class RoutedExpertsSpec:
+    """kind "routed_experts": ``experts`` small gated feed-forwards of which a token uses
+    ``top``, plus an optional shared one (``shared_size`` > 0) that every token uses.
+
+    Router logits are float.  ``score``: "sigmoid" or "softmax" over all experts.
+    ``renormalize``: the chosen scores are divided by their sum.  ``scale_input``: the
+    weight multiplies the expert's input (True) or its output (False).
+    """
+
+    kind: str = "routed_experts"
+    hidden_size: int = 0
+    num_experts: int = 0
+    top: int = 1
+    expert_size: int = 0
+    shared_size: int = 0
+    score: str = "sigmoid"
+    renormalize: bool = False
+    scale_input: bool = True
+    activation: str = "silu"
+
+
+@dataclass(frozen=True)
 class EmbeddingSpec:
     """kind "table": the residual starts as ``table[token] * multiplier`` in float."""
 
@@ -117,6 +191,8 @@ class BlockSpec:
     """One set of layer weights and how its parts are wired.
 
     kind "prenorm": ``h += mixer(norm1(h)); h += ffn(norm2(h))``.
+    kind "sandwich": ``h += norm1_post(mixer(norm1(h))); h += norm2_post(ffn(norm2(h)))``;
+    ``ffn`` None leaves the second sublayer (and its norms) out.
     ``mixer`` / ``ffn`` are any registered spec; they may differ from block
     to block within one model.
     """
@@ -125,7 +201,9 @@ class BlockSpec:
     mixer: object
     ffn: object
     norm1: NormSpec
-    norm2: NormSpec
+    norm2: Optional[NormSpec]
+    norm1_post: Optional[NormSpec] = None
+    norm2_post: Optional[NormSpec] = None
 
 
 @dataclass(frozen=True)

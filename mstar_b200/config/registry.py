@@ -1,6 +1,7 @@
 """One registry from an architecture's name to everything needed to run it.
 
-The name is ``config.json["architectures"][0]``.  The reference keys its
+The name is ``config.json["architectures"][0]``, or ``config.json["architecture"]``
+where a configuration names a single one.  The reference keys its
 registry by deployment name instead and raises KeyError with the known names
 (mstar/model/registry.py:8-41); the behaviour on an unknown name is kept.
 
@@ -55,8 +56,11 @@ def get_architecture(name: str) -> Architecture:
 
 def architecture_of(raw: Mapping[str, Any]) -> Architecture:
     names = raw.get("architectures")
+    if not names and isinstance(raw.get("architecture"), str):
+        names = [raw["architecture"]]               # some configurations name just one
     if not names or not isinstance(names, (list, tuple)):
-        raise ConfigError('config.json has no "architectures" list; cannot choose a model '
+        raise ConfigError('config.json has neither an "architectures" list nor an '
+                          '"architecture" name; cannot choose a model '
                           f"(known: {known_architectures()})")
     return get_architecture(str(names[0]))
 
@@ -84,3 +88,8 @@ def _register_builtin() -> None:
 
     if "LlamaForCausalLM" not in _ARCHITECTURES:
         register_architecture("LlamaForCausalLM", LlamaConfig, llama_checkpoint_map)
+    from ..weights.tifosun import tifosun_checkpoint_map
+    from .tifosun import TifosunConfig
+
+    if "Tifosun" not in _ARCHITECTURES:
+        register_architecture("Tifosun", TifosunConfig, tifosun_checkpoint_map)

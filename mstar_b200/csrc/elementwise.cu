@@ -517,3 +517,94 @@ MSTAR_API int mstar_rope_kv_write(void* qkv, int act_dtype, const int* positions
             (bf16*)qkv, positions, cache_pos, token_req, block_table, inv_freq, (bf16*)kv_cache, a);
     return launch_status();
 }
+
+// ------------------------------------------- post-norm + residual add + pre-norm
+// A sublayer whose output is normalised before it joins the residual:
+//   resid += rms(delta, post_eps) * (post_w + post_off)          (always)
+//   out    = rms(resid, eps) * (weight + w_off)                  (when out != nullptr)
+// One block per row; the row stays in shared memory between the passes.  Sums, scales and
+// the residual are float for both activation types; a row's sums are taken in an order that
+// depends only on its width.
+template <typename A, typename W>
+__global__ void add_postnorm_rmsnorm_kernel(float* __restrict__ resid, const A* __restrict__ delta,
+                                            const float* __restrict__ post_w, float post_eps,
+                                            float post_off, const W* __restrict__ weight,
+                                            A* __restrict__ out, int hidden, float eps, float w_off) {
+    extern __shared__ float row[];
+    __shared__ float scratch[32];
+    const size_t base = (size_t)blockIdx.x * hidden;
+    delta = pdl_after(delta, pdl_wait());
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float d = to_float(delta[base + i]);
+        row[i] = d;
+        ss = fmaf(d, d, ss);
+    }
+    const float inv_d = rsqrtf(block_sum(ss, scratch) / (float)hidden + post_eps);
+    float ss2 = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float h = resid[base + i] + row[i] * inv_d * (post_w[i] + post_off);
+        resid[base + i] = h;
+        row[i] = h;
+        ss2 = fmaf(h, h, ss2);
+    }
+    if (out == nullptr) return;
+    const float inv = rsqrtf(block_sum(ss2, scratch) / (float)hidden + eps);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+        out[base + i] = from_float<A>(row[i] * inv * (to_float(weight[i]) + w_off));
+}
+
+MSTAR_API int mstar_add_postnorm_rmsnorm(float* resid, const void* delta, const float* post_w,
+                                         float post_eps, float post_off, const void* weight,
+                                         int weight_dtype, void* out, int act_dtype, int rows,
+                                         int hidden, float eps, float w_off, void* stream) {
+    if (rows <= 0) return 0;
+    if (hidden <= 0 || hidden > 48 * 1024 / 4) return -1;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    const size_t smem = sizeof(float) * (size_t)hidden;
+#define LAUNCH(A, W)                                                                              \
+    mstar_launch((add_postnorm_rmsnorm_kernel<A, W>), dim3(rows), dim3(threads), smem, s, resid,  \
+                 (const A*)delta, post_w, post_eps, post_off, (const W*)weight, (A*)out, hidden,  \
+                 eps, w_off)
+    if (act_dtype == MSTAR_F32) {
+        if (weight_dtype == MSTAR_F32) { LAUNCH(float, float); } else { LAUNCH(float, bf16); }
+    } else {
+        if (weight_dtype == MSTAR_F32) { LAUNCH(bf16, float); } else { LAUNCH(bf16, bf16); }
+    }
+#undef LAUNCH
+    return launch_status();
+}
+
+// ------------------------------------------------------------ y *= sigmoid(gate)
+// y: [rows, cols] contiguous; gate: rows of `ldg` elements (a view into a wider product).
+template <typename A>
+__global__ void sigmoid_gate_mul_kernel(A* __restrict__ y, const A* __restrict__ gate, int cols,
+                                        int ldg, size_t total) {
+    const unsigned long long waited = pdl_wait();
+    y = pdl_after(y, waited);
+    gate = pdl_after(gate, waited);
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = idx / cols;
+        const int c = (int)(idx - r * cols);
+        const float g = to_float(gate[r * (size_t)ldg + c]);
+        y[idx] = from_float<A>(to_float(y[idx]) / (1.f + expf(-g)));
+    }
+}
+
+MSTAR_API int mstar_sigmoid_gate_mul(void* y, const void* gate, int act_dtype, int rows, int cols,
+                                     int ldg, void* stream) {
+    if (rows <= 0 || cols <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t total = (size_t)rows * cols;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < 4096 ? (total + threads - 1) / threads : 4096);
+    if (act_dtype == MSTAR_F32)
+        mstar_launch((sigmoid_gate_mul_kernel<float>), dim3(blocks), dim3(threads), 0, s, (float*)y,
+                     (const float*)gate, cols, ldg, total);
+    else
+        mstar_launch((sigmoid_gate_mul_kernel<bf16>), dim3(blocks), dim3(threads), 0, s, (bf16*)y,
+                     (const bf16*)gate, cols, ldg, total);
+    return launch_status();
+}

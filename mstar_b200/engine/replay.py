@@ -1,6 +1,6 @@
 """Trace replay: feed given token ids through a model step by step and write logits.
 
-    trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N
+    trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N [--max-requests R]
 
 Steps are read from standard input, one JSON object per line:
 
@@ -11,8 +11,9 @@ generation uses); nothing is sampled.  For a step that wants something, the floa
 logits [wanted, vocab] are written little-endian to ``<out>/<step>.f32``.  After
 every step ``done <step>`` is printed and flushed.  Requests named in ``end`` give
 back what they hold after the step.  The cache pool is sized for ``--max-tokens``
-tokens held by live requests, each request's count rounded up to whole pages, so
-that pages are reused.
+tokens held by live requests, each request's count rounded up to whole pages, and has
+``--max-requests`` state slots (four unless told otherwise), so that pages and slots are
+reused.
 
 The reference has no such program; its closest facility is reading back static
 logits in a CUDA-graph parity test (test/integration/test_prefill_cuda_graph.py:17-21).
@@ -25,7 +26,7 @@ import sys
 from pathlib import Path
 
 PAGE_SIZE = 16
-MAX_LIVE_REQUESTS = 64
+MAX_LIVE_REQUESTS = 4
 
 
 def build_parser() -> argparse.ArgumentParser:
@@ -35,6 +36,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--out", required=True, help="folder for <step>.f32 files")
     p.add_argument("--max-tokens", type=int, required=True,
                    help="most tokens that live requests hold at any time")
+    p.add_argument("--max-requests", type=int, default=MAX_LIVE_REQUESTS,
+                   help="most requests that are live at any time (state slots)")
     p.add_argument("--page-size", type=int, default=PAGE_SIZE)
     p.add_argument("--device", default="cuda:0")
     return p
@@ -56,7 +59,7 @@ def main(argv=None) -> int:
     # one spare page per live request covers a request's last, partly filled page
     pages = -(-args.max_tokens // args.page_size) + 0
     stepper = make_stepper(model, page_size=args.page_size, num_pages=max(pages, 1),
-                           num_slots=MAX_LIVE_REQUESTS)
+                           num_slots=max(args.max_requests, 1))
     print(f"[trace_run] ready: {pages} pages of {args.page_size} tokens", file=sys.stderr,
           flush=True)
 

@@ -703,3 +703,206 @@ def sample(logits: torch.Tensor, temperature, top_k=None, top_p=None, penalty=No
         _ptr(top_p), _ptr(penalty), _ptr(seen_mask), _ptr(seen_rows), _ptr(seed), _ptr(offset),
         out.data_ptr(), _stream()), "sample")
     return out
+
+
+# ------------------------------------------------------------------ sandwich norms
+def add_postnorm_rmsnorm(resid: torch.Tensor, delta: torch.Tensor, post_weight: torch.Tensor,
+                         post_eps: float, post_offset: float, weight=None, eps: float = 0.0,
+                         weight_offset: float = 0.0, out_dtype: torch.dtype | None = None):
+    """resid += rms(delta) * (post_weight + post_offset), in place in float; with ``weight``,
+    returns rms(resid) * (weight + weight_offset) in ``out_dtype`` (else None).
+    ``post_weight`` is a float vector."""
+    _need_cuda(resid, delta, post_weight, weight)
+    assert resid.dtype == torch.float32 and resid.dim() == 2 and resid.is_contiguous()
+    assert delta.shape == resid.shape and delta.is_contiguous()
+    assert post_weight.dtype == torch.float32 and post_weight.numel() == resid.shape[1]
+    rows, hidden = resid.shape
+    out = None
+    if weight is not None:
+        assert weight.numel() == hidden and weight.is_contiguous()
+        out_dtype = out_dtype or delta.dtype
+        assert out_dtype == delta.dtype
+        out = torch.empty((rows, hidden), dtype=out_dtype, device=resid.device)
+    code = lib.get("elementwise").mstar_add_postnorm_rmsnorm(
+        resid.data_ptr(), delta.data_ptr(), post_weight.data_ptr(), float(post_eps),
+        float(post_offset), _ptr(weight), _dt(weight) if weight is not None else F32, _ptr(out),
+        _dt(delta), rows, hidden, float(eps), float(weight_offset), _stream())
+    if code == -1:
+        raise KernelError(f"post-norm kernel refuses a width of {hidden}")
+    check(code, "add_postnorm_rmsnorm")
+    return out
+
+
+def sigmoid_gate_mul(y: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """In place: y *= sigmoid(gate).  ``gate`` may be a column view of a wider product."""
+    _need_cuda(y, gate)
+    assert y.dim() == 2 and y.is_contiguous() and gate.shape == y.shape and gate.stride(1) == 1
+    assert gate.dtype == y.dtype
+    check(lib.get("elementwise").mstar_sigmoid_gate_mul(
+        y.data_ptr(), gate.data_ptr(), _dt(y), y.shape[0], y.shape[1], gate.stride(0), _stream()),
+        "sigmoid_gate_mul")
+    return y
+
+
+# ------------------------------------------------------------------ matrix memory
+def matrix_memory_state_size(heads: int, dim: int, vdim: int) -> int:
+    """Floats of one request's state: S^T [heads, vdim, dim], n [heads, dim], m [heads]."""
+    return heads * (dim * vdim + dim + 1)
+
+
+def matrix_memory_scan(proj: torch.Tensor, gates: torch.Tensor, bias: torch.Tensor, qo_indptr,
+                       slots, state: torch.Tensor, entries: int, heads: int, dim: int, vdim: int,
+                       cap: float, q_scale: float, floor: float) -> torch.Tensor:
+    """The mLSTM recurrence over the tokens of ``entries`` batch entries, each continuing
+    the state in its slot (updated in place).  ``proj``: [tokens, >= 2*heads*dim + heads*vdim]
+    with q, k, v side by side; ``gates``: float [tokens, 2*heads] pre-activations (input gates
+    first), ``bias`` float [2*heads].  Returns float [tokens, heads*vdim]."""
+    _need_cuda(proj, gates, bias, qo_indptr, slots, state)
+    assert proj.dim() == 2 and proj.stride(1) == 1
+    assert gates.dtype == torch.float32 and gates.is_contiguous() and gates.shape[1] == 2 * heads
+    assert bias.dtype == torch.float32 and bias.numel() == 2 * heads
+    assert state.dtype == torch.float32 and state.dim() == 2 and state.is_contiguous()
+    tokens = proj.shape[0]
+    out = torch.empty((tokens, heads * vdim), dtype=torch.float32, device=proj.device)
+    code = lib.get("matrix_memory").mstar_matrix_memory_scan(
+        proj.data_ptr(), _dt(proj), proj.stride(0), heads * dim, 2 * heads * dim, gates.data_ptr(),
+        bias.data_ptr(), qo_indptr.data_ptr(), slots.data_ptr(), state.data_ptr(),
+        state.stride(0), out.data_ptr(), entries, heads, dim, vdim, float(cap), float(q_scale),
+        float(floor), _stream())
+    if code == -1:
+        raise KernelError(f"matrix-memory scan refuses heads={heads}, dim={dim}, vdim={vdim} "
+                          "(dim at most 512)")
+    check(code, "matrix_memory_scan")
+    return out
+
+
+def head_norm_gate(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, heads: int,
+                   vdim: int, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """o / rms(o per head) * weight * sigmoid(gate): float ``o`` [tokens, heads*vdim], ``gate``
+    a column view in ``out_dtype``, float ``weight`` [heads*vdim]."""
+    _need_cuda(o, gate, weight)
+    assert o.dtype == torch.float32 and o.is_contiguous() and weight.dtype == torch.float32
+    assert gate.dtype == out_dtype and gate.stride(1) == 1 and gate.shape == o.shape
+    out = torch.empty(o.shape, dtype=out_dtype, device=o.device)
+    check(lib.get("matrix_memory").mstar_head_norm_gate(
+        o.data_ptr(), gate.data_ptr(), gate.stride(0), weight.data_ptr(), out.data_ptr(), _dt(out),
+        o.shape[0], heads, vdim, float(eps), _stream()), "head_norm_gate")
+    return out
+
+
+# ------------------------------------------------------------------ latent attention
+def latent_fill(proj: torch.Tensor, dkv_offset: int, norm_weight: torch.Tensor, freq: torch.Tensor,
+                positions, cache_pos, token_req, block_table, cache: torch.Tensor, heads: int,
+                qk_dim: int, rot: int, rot_dims: int, rank: int, page_size: int, eps: float) -> None:
+    """Normalise the latent part of the down-projection, rotate the shared key part and write
+    both into the token's cache row; rotate the rotated part of every query head in place.
+    ``proj``: [tokens, ...] with the queries at column 0 (head by head: qk_dim plain, rot
+    rotated features) and the down-projection at ``dkv_offset``; ``cache``: [pages, 1, 1,
+    page_size, rank + rot]; ``freq``: float64 [rot_dims / 2]."""
+    _need_cuda(proj, norm_weight, freq, positions, cache_pos, token_req, block_table, cache)
+    assert proj.dim() == 2 and proj.stride(1) == 1 and cache.dtype == proj.dtype
+    assert cache.is_contiguous() and tuple(cache.shape[1:]) == (1, 1, page_size, rank + rot)
+    assert norm_weight.dtype == torch.float32 and norm_weight.numel() == rank
+    assert freq.dtype == torch.float64 and freq.numel() == rot_dims // 2
+    code = lib.get("attention_latent").mstar_latent_fill(
+        proj.data_ptr(), _dt(proj), proj.stride(0), dkv_offset, norm_weight.data_ptr(),
+        freq.data_ptr(), positions.data_ptr(), cache_pos.data_ptr(), token_req.data_ptr(),
+        block_table.data_ptr(), block_table.stride(0), cache.data_ptr(), proj.shape[0], heads,
+        qk_dim, rot, rot_dims, rank, page_size, float(eps), _stream())
+    if code == -1:
+        raise KernelError(f"latent cache fill refuses rot_dims={rot_dims} of rot={rot}")
+    check(code, "latent_fill")
+
+
+def latent_attention(q_abs: torch.Tensor, q_rot: torch.Tensor, cache: torch.Tensor, block_table,
+                     token_req, cache_pos, heads: int, rank: int, rot: int, page_size: int,
+                     window: int, scale: float) -> torch.Tensor:
+    """Softmax attention of every token over the latent rows it sees.  ``q_abs``: float
+    [tokens, heads, rank], the plain query part with the key up-projection folded in;
+    ``q_rot``: [tokens, heads, rot] view (last stride 1) of rotated query parts.  Returns the
+    float [tokens, heads, rank] probability-weighted sums of latents."""
+    _need_cuda(q_abs, q_rot, cache, block_table, token_req, cache_pos)
+    assert q_abs.dtype == torch.float32 and q_abs.is_contiguous()
+    tokens = q_abs.shape[0]
+    assert tuple(q_abs.shape) == (tokens, heads, rank) and cache.is_contiguous()
+    assert tuple(q_rot.shape) == (tokens, heads, rot) and q_rot.dtype == cache.dtype
+    assert rot == 0 or q_rot.stride(2) == 1
+    out = torch.empty((tokens, heads, rank), dtype=torch.float32, device=q_abs.device)
+    code = lib.get("attention_latent").mstar_latent_attention(
+        q_abs.data_ptr(), q_rot.data_ptr(), q_rot.stride(0), q_rot.stride(1), out.data_ptr(),
+        cache.data_ptr(), block_table.data_ptr(), block_table.stride(0), token_req.data_ptr(),
+        cache_pos.data_ptr(), tokens, heads, rank, rot, page_size, int(window or 0), float(scale),
+        _dt(cache), _stream())
+    if code == -1:
+        raise KernelError(f"latent attention refuses rank={rank}, rot={rot} (rank at most 4096, "
+                          "a tile of 32 rows within 200 KB of shared memory)")
+    check(code, "latent_attention")
+    return out
+
+
+def linear_per_head(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None):
+    """out[t, h, :] = x[t, h, :] @ w[h]^T for x [tokens, heads, K] (any token and head strides,
+    last stride 1) and w [heads, N, K].  bfloat16: the library's batched GEMM; float32: this
+    package's true-32-bit kernel, head by head."""
+    _need_cuda(x, w)
+    tokens, heads, k = x.shape
+    assert w.shape[0] == heads and w.shape[2] == k and x.stride(2) == 1 and w.is_contiguous()
+    n = w.shape[1]
+    out_dtype = out_dtype or x.dtype
+    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+        a, b = x.transpose(0, 1), w.transpose(1, 2)
+        if out_dtype == torch.float32:
+            try:
+                return torch.bmm(a, b, out_dtype=torch.float32).transpose(0, 1).contiguous()
+            except (TypeError, RuntimeError):
+                return torch.bmm(a, b).transpose(0, 1).float()
+        return torch.bmm(a, b).transpose(0, 1).contiguous()
+    xf = x if x.dtype == torch.float32 else x.float()
+    wf = w if w.dtype == torch.float32 else w.float()
+    out = torch.empty((tokens, heads, n), dtype=torch.float32, device=x.device)
+    for h in range(heads):
+        sgemm_nt(xf[:, h], wf[h], out[:, h])
+    return out if out_dtype == torch.float32 else convert(out, out_dtype)
+
+
+# ------------------------------------------------------------------ routed experts
+def route_topk(logits: torch.Tensor, top: int, softmax: bool = False, renormalize: bool = False):
+    """(chosen int32 [tokens, top], weight float [tokens, top]) from float router logits."""
+    _need_cuda(logits)
+    assert logits.dtype == torch.float32 and logits.dim() == 2 and logits.is_contiguous()
+    tokens, experts = logits.shape
+    chosen = torch.empty((tokens, top), dtype=torch.int32, device=logits.device)
+    weight = torch.empty((tokens, top), dtype=torch.float32, device=logits.device)
+    code = lib.get("routed_experts").mstar_route_topk(
+        logits.data_ptr(), chosen.data_ptr(), weight.data_ptr(), tokens, experts, top,
+        int(softmax), int(renormalize), _stream())
+    if code == -1:
+        raise KernelError(f"cannot choose {top} of {experts} experts")
+    check(code, "route_topk")
+    return chosen, weight
+
+
+def experts_by_row(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, chosen, weight,
+                   ff: int, scale_input: bool, add=None) -> torch.Tensor:
+    """sum over a token's chosen experts of down(silu(gate u) * up u) (+ ``add``), every row
+    streaming its experts' matrices.  ``w_gate_up``: [experts * 2 * ff, width] (per expert
+    gate rows, then up rows), ``w_down``: [experts * width, ff]."""
+    _need_cuda(x, w_gate_up, w_down, chosen, weight, add)
+    tokens, width = x.shape
+    top = chosen.shape[1]
+    assert x.is_contiguous() and w_gate_up.is_contiguous() and w_down.is_contiguous()
+    assert w_gate_up.dtype == x.dtype and w_down.dtype == x.dtype
+    assert w_gate_up.shape[1] == width and w_down.shape[1] == ff
+    assert add is None or (add.shape == x.shape and add.is_contiguous() and add.dtype == x.dtype)
+    act = torch.empty((tokens * top, ff), dtype=torch.float32, device=x.device)
+    out = torch.empty_like(x)
+    code = lib.get("routed_experts").mstar_experts_by_row(
+        x.data_ptr(), w_gate_up.data_ptr(), w_down.data_ptr(), chosen.data_ptr(),
+        weight.data_ptr(), act.data_ptr(), _ptr(add), out.data_ptr(), _dt(x), tokens, width, ff,
+        top, int(scale_input), _stream())
+    if code == -1:
+        raise KernelError(f"the by-row expert kernels refuse width={width}, ff={ff}, top={top} "
+                          "(a row of inputs, and of hidden units, within 48 KB)")
+    check(code, "experts_by_row")
+    lib.add_launches(1)                       # two kernels behind one call
+    return out

@@ -41,6 +41,9 @@ LIBRARIES = {
     "gemm_tcgen05": ("cuda", ["gemm_tcgen05.cu"], []),
     "gemm_skinny": ("cuda", ["gemm_skinny.cu"], []),
     "sampling": ("cuda", ["sampling.cu"], []),
+    "matrix_memory": ("cuda", ["matrix_memory.cu"], []),
+    "attention_latent": ("cuda", ["attention_latent.cu"], []),
+    "routed_experts": ("cuda", ["routed_experts.cu"], []),
     "host": ("host", ["host/cache_manager.cpp"], []),
 }
 

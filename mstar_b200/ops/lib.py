@@ -27,6 +27,25 @@ _SIGNATURES = {
         "mstar_convert": [_vp, _i, _vp, _i, _ll, _vp],
         "mstar_rope_kv_write": [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i,
                                 _i, _i, _vp],
+        "mstar_add_postnorm_rmsnorm": [_vp, _vp, _vp, _f, _f, _vp, _i, _vp, _i, _i, _i, _f, _f,
+                                       _vp],
+        "mstar_sigmoid_gate_mul": [_vp, _vp, _i, _i, _i, _i, _vp],
+    },
+    "matrix_memory": {
+        "mstar_matrix_memory_scan": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _i,
+                                     _i, _i, _i, _f, _f, _f, _vp],
+        "mstar_head_norm_gate": [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _f, _vp],
+    },
+    "attention_latent": {
+        "mstar_latent_attention": [_vp, _vp, _i, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i,
+                                   _i, _i, _f, _i, _vp],
+        "mstar_latent_fill": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i,
+                              _i, _i, _i, _i, _f, _vp],
+    },
+    "routed_experts": {
+        "mstar_route_topk": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+        "mstar_experts_by_row": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
+                                 _vp],
     },
     "attention_generic": {
         "mstar_paged_attention_generic": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i,

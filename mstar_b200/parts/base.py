@@ -10,12 +10,14 @@ import torch
 
 @dataclass(frozen=True)
 class KVNeed:
-    """Keys and values in pages: [pages, 2, num_kv_heads, page_size, head_dim].
-    ``window`` None keeps every key; W keeps the last W."""
+    """Keys and values in pages: [pages, planes, num_kv_heads, page_size, head_dim].
+    ``window`` None keeps every key; W keeps the last W.  ``planes``: 2 for keys and values,
+    1 for a mixer that keeps one row per token (a latent that both are made from)."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    planes: int = 2
 
 
 @dataclass(frozen=True)
@@ -45,7 +47,7 @@ class Runtime:
 class LayerCache:
     """The cache of one run-order entry, as its mixer sees it."""
 
-    kv: Optional[torch.Tensor] = None           # [pages, 2, kv_heads, page_size, head_dim]
+    kv: Optional[torch.Tensor] = None           # [pages, planes, kv_heads, page_size, head_dim]
     page_size: int = 0
     block_table: Optional[torch.Tensor] = None  # int32 [entries, width] of the cache's group
     state: Optional[torch.Tensor] = None        # [slots, *shape]
@@ -86,18 +88,38 @@ class StepContext:
 class ResidualStream:
     """The float residual ``h`` and the not-yet-added output ``delta`` of the last
     part.  Norm parts fold ``h += delta`` into the normalisation that follows, so
-    the residual sum is a 32-bit sum and costs no pass of its own."""
+    the residual sum is a 32-bit sum and costs no pass of its own.  A delta may be pushed
+    with a norm of its own (``post``: a norm part), which is applied to it on its way into
+    the residual: ``h += post(delta)``."""
 
     def __init__(self, h: torch.Tensor):
         assert h.dtype == torch.float32
         self.h = h
         self.delta: Optional[torch.Tensor] = None
+        self.post = None
 
-    def push(self, delta: torch.Tensor) -> None:
+    def push(self, delta: torch.Tensor, post=None) -> None:
         if self.delta is not None:
             raise RuntimeError("a part's output was pushed before the previous one was added")
         self.delta = delta
+        self.post = post
 
     def take_delta(self) -> Optional[torch.Tensor]:
+        """The pending delta as it is to be added.  One that carries a norm of its own is
+        added here and now (by that norm part), and nothing is left pending."""
+        if self.post is not None:
+            self.settle()
         d, self.delta = self.delta, None
         return d
+
+    def take_pending(self):
+        """(delta, its own norm part or None), for a norm that folds both in itself."""
+        d, post = self.delta, self.post
+        self.delta = self.post = None
+        return d, post
+
+    def settle(self) -> None:
+        """Add a pending delta that carries its own norm into ``h`` now."""
+        if self.delta is not None and self.post is not None:
+            d, post = self.take_pending()
+            post.add_normed(self.h, d)

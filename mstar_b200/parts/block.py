@@ -49,4 +49,51 @@ class PreNormBlock:
         stream.push(self.ffn.forward(y, ctx))
 
 
+class SandwichBlock:
+    """h += norm1_post(mixer(norm1(h))); h += norm2_post(ffn(norm2(h))).  A sublayer's output
+    is pushed together with its own norm; the next norm on the stream (this block's norm2, the
+    next block's norm1, or the model's final norm) applies it, adds and normalises in one
+    kernel.  A block without a feed-forward has the first sublayer only."""
+
+    @staticmethod
+    def _subparts(spec):
+        parts = [("norm1", "norm"), ("mixer", "mixer"), ("norm1_post", "norm")]
+        if spec.ffn is not None:
+            parts += [("norm2", "norm"), ("ffn", "ffn"), ("norm2_post", "norm")]
+        return parts
+
+    @classmethod
+    def param_specs(cls, spec) -> dict:
+        out = {}
+        for name, category in cls._subparts(spec):
+            sub = getattr(spec, name)
+            if sub is None:
+                raise ValueError(f"a sandwich block needs {name}")
+            for local, ps in part_class(category, sub).param_specs(sub).items():
+                out[f"{name}.{local}"] = ps
+        return out
+
+    @classmethod
+    def cache_need(cls, spec):
+        return part_class("mixer", spec.mixer).cache_need(spec.mixer)
+
+    def __init__(self, spec, params: dict, runtime: Runtime):
+        self.spec = spec
+        self.parts = {name: build_part(category, getattr(spec, name), _sub(params, name), runtime)
+                      for name, category in self._subparts(spec)}
+        self.norm1, self.mixer, self.norm1_post = (self.parts[k] for k in
+                                                   ("norm1", "mixer", "norm1_post"))
+        self.norm2, self.ffn, self.norm2_post = (self.parts.get(k) for k in
+                                                 ("norm2", "ffn", "norm2_post"))
+        self.graph_safe = all(getattr(p, "graph_safe", False) is True for p in self.parts.values())
+
+    def forward(self, stream: ResidualStream, ctx, cache) -> None:
+        x = self.norm1.add_norm(stream)
+        stream.push(self.mixer.forward(x, ctx, cache), post=self.norm1_post)
+        if self.ffn is not None:
+            y = self.norm2.add_norm(stream)
+            stream.push(self.ffn.forward(y, ctx), post=self.norm2_post)
+
+
 register_part("block", "prenorm", PreNormBlock)
+register_part("block", "sandwich", SandwichBlock)

@@ -22,7 +22,9 @@ class RMSNorm:
 
     @classmethod
     def param_specs(cls, spec) -> dict:
-        return {"weight": ParamSpec(shape=(spec.size,), role="vector", init="ones")}
+        # a weight stored as an offset from one starts at zero
+        return {"weight": ParamSpec(shape=(spec.size,), role="vector",
+                                    init="zeros" if spec.weight_offset else "ones")}
 
     def __init__(self, spec, params: dict, runtime: Runtime):
         self.spec = spec
@@ -32,9 +34,28 @@ class RMSNorm:
             raise ValueError(f"rmsnorm weight has shape {tuple(self.weight.shape)}, "
                              f"expected ({spec.size},)")
 
+    def _float_weight(self) -> torch.Tensor:
+        if getattr(self, "_weight_f32", None) is None:
+            self._weight_f32 = self.weight.float().contiguous()
+        return self._weight_f32
+
+    def add_normed(self, resid: torch.Tensor, delta: torch.Tensor) -> None:
+        """resid += norm(delta): this norm applied to a part's output on its way into the
+        float residual (the norm after a sublayer)."""
+        ops.add_postnorm_rmsnorm(resid, delta, self._float_weight(), self.spec.eps,
+                                 self.spec.weight_offset)
+
     def add_norm(self, stream: ResidualStream) -> torch.Tensor:
         """Fold the pending delta into the residual and return the normed rows."""
-        delta = stream.take_delta()
+        delta, post = stream.take_pending()
+        if post is not None:
+            if isinstance(post, RMSNorm):
+                # the sublayer's own norm, the residual sum and this norm as one kernel
+                return ops.add_postnorm_rmsnorm(
+                    stream.h, delta, post._float_weight(), post.spec.eps, post.spec.weight_offset,
+                    self.weight, self.spec.eps, self.spec.weight_offset, self.runtime.dtype)
+            post.add_normed(stream.h, delta)
+            delta = None
         # a pending delta is the output of the part before: its kernels lie between this
         # norm and whatever wrote the residual last
         return ops.add_rmsnorm(stream.h, delta, self.weight, self.spec.eps, self.runtime.dtype,

@@ -70,4 +70,5 @@ def _builtin() -> None:
     if _done:
         return
     _done = True
-    from . import attention, block, embedding, mlp, norm, rope  # noqa: F401  (they register themselves)
+    from . import (attention, block, embedding, latent_attention, matrix_memory, mlp, norm,  # noqa: F401
+                   rope, routed_experts)   # (they register themselves)

@@ -204,11 +204,12 @@ def run_steps_in_process(stepper, steps: list, device_fed_seed=None, keep=None) 
 
 
 def run_steps_with_trace_run(model_dir, dtype: str, steps: list, out_dir, vocab: int,
-                             max_tokens: int) -> dict:
+                             max_tokens: int, max_requests: int = 8) -> dict:
     """Drive bin/trace_run as a user would: one JSON line per step on stdin, wait for
     ``done <step>`` before the next."""
     cmd = [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(model_dir),
-           "--dtype", dtype, "--out", str(out_dir), "--max-tokens", str(max_tokens)]
+           "--dtype", dtype, "--out", str(out_dir), "--max-tokens", str(max_tokens),
+           "--max-requests", str(max_requests)]
     proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True)
     try:
         for i, st in enumerate(steps):
