@@ -101,7 +101,7 @@ def latent_attention_mixer(h, w, pre, cfg, eps, positions, past=None):
     """h: [T, width] at ``positions``; past: None or (c, kr) of the earlier tokens, in order.
     Returns (output, (c, kr) of all tokens so far)."""
     H, dim, rot, vdim, rank = cfg["heads"], cfg["dim"], cfg["rot_dim"], cfg["vdim"], cfg["kv_rank"]
-    window = cfg["mask"]["size"]
+    window = cfg["mask"]["size"] if cfg.get("mask") else None       # None: every key
     T = h.shape[0]
     q = (h @ w[pre + "q"].T).view(T, H, dim + rot)
     q_plain = q[..., :dim]
@@ -116,7 +116,7 @@ def latent_attention_mixer(h, w, pre, cfg, eps, positions, past=None):
     out = torch.zeros(T, H, vdim, dtype=F64)
     for t in range(T):
         i = first + t
-        lo = max(0, i - window + 1)
+        lo = 0 if window is None else max(0, i - window + 1)
         for hh in range(H):
             s = (k_plain[lo:i + 1, hh] @ q_plain[t, hh] + kr[lo:i + 1] @ q_rot[t, hh]) * cfg["scale"]
             p = torch.softmax(s, dim=0)
