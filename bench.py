@@ -5,6 +5,7 @@ one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--rounds R] [--page-size P]
                     [--impl ours|reference] [--workloads all|none|mixed64|long8]
+    python bench.py --arch tifosun [--arch-size small|medium]     (another architecture)
 
 One JSON line on stdout.  ``value``: decoded tokens per second of the engine's step
 function plus greedy sampling, timed on the device with CUDA events: W warm-up steps, then
@@ -335,6 +336,193 @@ def run_workload(name: str, page_size: int) -> dict:
     return result
 
 
+# ------------------------------------------------------------------ another architecture
+def tifosun_sizes(name: str) -> tuple:
+    """(Tifosun config, Llama config of equal size) at layer sizes that resemble a real
+    model's: three matrix-memory layers to one windowed latent-attention layer, routed
+    experts with a shared one in most layers and a dense feed-forward in the first.  The
+    Llama beside it has the same width, depth and vocabulary, heads of 128, and a
+    feed-forward as wide as the experts a Tifosun token uses (top experts + shared)."""
+    if name == "small":
+        width, depth, vocab = 1024, 8, 32000
+        mem = dict(heads=4, dim=128, vdim=256, gate_cap=15.0)
+        att = dict(heads=8, dim=64, rot_dim=32, vdim=128, kv_rank=256, mask={"size": 512},
+                   rot={"base": 10000.0, "dims": 32}, scale=96 ** -0.5)
+        experts, top, ff, shared, dense = 16, 2, 512, 1024, 3072
+    elif name == "medium":
+        width, depth, vocab = 2048, 12, 64000
+        mem = dict(heads=4, dim=256, vdim=512, gate_cap=15.0)
+        att = dict(heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512, mask={"size": 1024},
+                   rot={"base": 10000.0, "dims": 64}, scale=192 ** -0.5)
+        experts, top, ff, shared, dense = 32, 4, 768, 2048, 6144
+    else:
+        raise ValueError(f"unknown size {name!r} (small, medium)")
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff},
+           "shared": {"ff": shared}}
+    layers = []
+    for i in range(depth):
+        kind = "latent_attention" if i % 4 == 2 else ("mlstm_2" if i % 4 == 3 else "mlstm")
+        layers.append({"type": kind, "mixer": dict(att if kind == "latent_attention" else mem),
+                       "mlp": {"kind": "dense", "ff": dense} if i == 0 else moe})
+    tifosun = {"architecture": "Tifosun", "width": width, "vocab": vocab, "norm": {"eps": 1e-6},
+               "layers": layers}
+    llama = dict(ORPHEUS_3B, num_hidden_layers=depth, hidden_size=width,
+                 num_attention_heads=width // 128, num_key_value_heads=max(width // 512, 1),
+                 head_dim=128, intermediate_size=top * ff + shared, vocab_size=vocab,
+                 tie_word_embeddings=False)
+    return tifosun, llama
+
+
+def arch_bench(args) -> int:
+    """``--arch tifosun``: prefill and decode throughput of the Tifosun decoder (random
+    weights, bfloat16) at ``--arch-size``, beside the Llama decoder at equal size, through the
+    same step function; and its own kernels alone at those sizes with what each has to move
+    or compute, against the measured peaks.  One JSON line."""
+    import torch
+
+    from mstar_b200 import ops
+    from mstar_b200.engine.step import make_stepper
+
+    pk = peaks()
+    t_cfg, l_cfg = tifosun_sizes(args.arch_size)
+    page, batch = args.page_size, args.batch
+    out = {"arch": "Tifosun", "size": args.arch_size, "batch": batch, "prompt_len": PROMPT_LEN,
+           "peaks": pk["source"], "models": {}, "kernels": {}}
+    for name, raw in (("tifosun", t_cfg), ("llama", l_cfg)):
+        print(f"[bench] {name} at the {args.arch_size} sizes ...", file=sys.stderr, flush=True)
+        model = build_model(raw)
+        cfg = {"vocab_size": model.vocab_size}
+        stepper = make_stepper(model, page_size=page, num_pages=batch * (CONTEXT // page) + 64,
+                               num_slots=batch + 4)
+        toks = prompts(7, model.vocab_size, PROMPT_LEN, seed=99)
+        times = []
+        for i, t in enumerate(toks):
+            from mstar_b200.engine.step import StepEntry
+            stepper.add_request(f"p{i}")
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            start.record()
+            stepper.step([StepEntry(f"p{i}", t, (PROMPT_LEN - 1,))])
+            end.record()
+            torch.cuda.synchronize()
+            stepper.free_request(f"p{i}")
+            if i >= 2:
+                times.append(start.elapsed_time(end))
+        pre_ms = statistics.median(times)
+        dec = time_decode(stepper, batch, cfg, args.steps, max(args.warmup, 3), min(args.rounds, 3))
+        out["models"][name] = {
+            "parameters_gb": round(model.parameter_bytes() / 1e9, 3),
+            "prefill_ms": round(pre_ms, 3), "prefill_tok_s": round(PROMPT_LEN / pre_ms * 1e3, 1),
+            "decode_ms_per_step": round(dec["ms_per_step"], 4),
+            "decode_tok_s": round(dec["tokens_per_s"], 1), "launches_per_step": dec["launches"] // args.steps}
+        del stepper, model
+        torch.cuda.empty_cache()
+
+    # ---- the new kernels alone, at the sizes of one layer
+    dev = "cuda:0"
+    g = torch.Generator(device=dev).manual_seed(0)
+
+    def rnd(*shape, scale=1.0):
+        return (scale * torch.randn(*shape, generator=g, device=dev)).to(torch.bfloat16)
+
+    def i32(v):
+        return torch.tensor(v, dtype=torch.int32, device=dev)
+
+    width = t_cfg["width"]
+    mem = next(l["mixer"] for l in t_cfg["layers"] if l["type"] == "mlstm")
+    att = next(l["mixer"] for l in t_cfg["layers"] if l["type"] == "latent_attention")
+    moe = next(l["mlp"] for l in t_cfg["layers"] if l["mlp"]["kind"] == "moe")
+    K = out["kernels"]
+    H, dim, vdim = mem["heads"], mem["dim"], mem["vdim"]
+    size = ops.matrix_memory_state_size(H, dim, vdim)
+    copies = max(1, -(-(160 << 20) // (size * 4 * batch)))          # states larger than L2
+    state = torch.zeros(copies * batch + 1, size, device=dev)
+    for tokens, entries, label in ((batch, batch, "decode"), (PROMPT_LEN, 1, "prefill")):
+        proj = rnd(tokens, 2 * H * dim + 2 * H * vdim)
+        gates = torch.randn(tokens, 2 * H, device=dev)
+        bias = torch.zeros(2 * H, device=dev)
+        per = tokens // entries
+        indptr = i32([k * per for k in range(entries + 1)])
+        turn = {"i": 0}
+
+        def scan():
+            base = (turn["i"] % copies) * batch
+            turn["i"] += 1
+            return ops.matrix_memory_scan(proj, gates, bias, indptr, slot_sets[base // batch],
+                                          state, entries, H, dim, vdim, 15.0, dim ** -0.5, 1e-6)
+
+        slot_sets = [i32([c * batch + k for k in range(entries)]) for c in range(copies)]
+        ms = _time_graph(scan, reps=max(copies, 4) if label == "decode" else 2)
+        nbytes = 2.0 * entries * size * 4
+        K[f"matrix_memory_scan_{label}"] = {
+            "ms": round(ms, 4), "state_gbs": round(nbytes / ms / 1e6, 1),
+            "frac_hbm": round(nbytes / ms / 1e6 / pk["hbm_gbs"], 4),
+            "tokens_per_chain_us": round(per / (ms * 1e3), 3)}
+    heads, rank, rot, window = att["heads"], att["kv_rank"], att["rot_dim"], att["mask"]["size"]
+    for tokens, reqs, label in ((batch, batch, "decode"), (PROMPT_LEN, 1, "prefill")):
+        ctx = PROMPT_LEN
+        pages_per = -(-ctx // page)
+        copies = 1 if label == "prefill" else max(1, -(-(160 << 20) // (reqs * window * (rank + rot) * 2)))
+        caches = [rnd(reqs * pages_per + 1, 1, 1, page, rank + rot) for _ in range(copies)]
+        table = torch.randperm(reqs * pages_per, device=dev).to(torch.int32).view(reqs, pages_per)
+        per = tokens // reqs
+        token_req = i32([r for r in range(reqs) for _ in range(per)])
+        cache_pos = i32([ctx - per + k for _ in range(reqs) for k in range(per)])
+        q_abs = torch.randn(tokens, heads, rank, device=dev)
+        q_rot = rnd(tokens, heads, rot)
+        turn = {"i": 0}
+
+        def attend():
+            c = caches[turn["i"] % copies]
+            turn["i"] += 1
+            return ops.latent_attention(q_abs, q_rot, c, table, token_req, cache_pos, heads, rank,
+                                        rot, page, window, att["scale"])
+
+        ms = _time_graph(attend, reps=max(copies, 4) if label == "decode" else 2)
+        keys = sum(min(ctx - per + k + 1, window) for k in range(per)) * reqs
+        flops = 2.0 * heads * keys * (2 * rank + rot)
+        nbytes = reqs * min(ctx, window + per) * (rank + rot) * 2.0
+        K[f"latent_attention_{label}"] = {
+            "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 2),
+            "frac_bf16": round(flops / ms / 1e9 / pk["bf16_tflops"], 5),
+            "gbs": round(nbytes / ms / 1e6, 1), "frac_hbm": round(nbytes / ms / 1e6 / pk["hbm_gbs"], 4)}
+    E, top, ff = moe["router"]["experts"], moe["router"]["top"], moe["expert"]["ff"]
+    copies = max(1, -(-(160 << 20) // (E * 3 * ff * width * 2)))
+    w_gu = [rnd(E * 2 * ff, width, scale=0.02) for _ in range(copies)]
+    w_dn = [rnd(E * width, ff, scale=0.02) for _ in range(copies)]
+    for tokens, label in ((batch, "decode"), (PROMPT_LEN, "prefill")):
+        x = rnd(tokens, width)
+        chosen, weight = ops.route_topk(torch.randn(tokens, E, device=dev), top)
+        turn = {"i": 0}
+
+        def experts():
+            k = turn["i"] % copies
+            turn["i"] += 1
+            return ops.routed_experts(x, w_gu[k], w_dn[k], chosen, weight, E, ff, True)
+
+        ms = _time_graph(experts, reps=max(copies * 2, 4) if label == "decode" else 2)
+        used = len(set(chosen.flatten().tolist()))
+        nbytes = used * 3.0 * ff * width * 2
+        flops = 2.0 * tokens * top * 3 * ff * width
+        K[f"routed_experts_{label}"] = {
+            "ms": round(ms, 4), "experts_used": used, "gbs": round(nbytes / ms / 1e6, 1),
+            "frac_hbm": round(nbytes / ms / 1e6 / pk["hbm_gbs"], 4),
+            "tflops": round(flops / ms / 1e9, 2),
+            "frac_bf16": round(flops / ms / 1e9 / pk["bf16_tflops"], 5)}
+    for tokens, label in ((batch, "decode"), (PROMPT_LEN, "prefill")):
+        resid = torch.randn(tokens, width, device=dev)
+        delta, w = rnd(tokens, width), rnd(width)
+        wb = torch.randn(width, device=dev)
+        ms = _time_graph(lambda: ops.add_postnorm_rmsnorm(resid, delta, wb, 1e-6, 1.0, w, 1e-6, 1.0,
+                                                          torch.bfloat16), reps=20)
+        nbytes = tokens * width * (4 + 4 + 2 + 2.0)
+        K[f"postnorm_add_norm_{label}"] = {"ms": round(ms, 4), "gbs": round(nbytes / ms / 1e6, 1),
+                                           "frac_hbm": round(nbytes / ms / 1e6 / pk["hbm_gbs"], 4)}
+    ops.check_error_word(dev)
+    print(json.dumps(out))
+    return 0
+
+
 # --------------------------------------------------------------- single kernels
 def _time_graph(fn, reps: int = 20, rounds: int = 5) -> float:
     """Median milliseconds of one call of ``fn`` when ``reps`` calls are replayed as one
@@ -537,12 +725,18 @@ def main() -> int:
     ap.add_argument("--small", action="store_true", help="a smaller case, for profiler captures")
     ap.add_argument("--sizes", default="orpheus-3b", choices=sorted(SIZES),
                     help="layer sizes; the default is the benchmark model")
+    ap.add_argument("--arch", default=None, choices=["tifosun"],
+                    help="measure another architecture beside the Llama decoder at equal size "
+                         "(prefill, decode, its own kernels) instead of the headline workload")
+    ap.add_argument("--arch-size", default="small", choices=["small", "medium"])
     args = ap.parse_args()
     model_name, sizes = SIZES[args.sizes]
     PAGE_SIZE = page = args.page_size
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported")
         return 2
+    if args.arch:
+        return arch_bench(args)
     if args.kernel:
         return kernel_bench(args.kernel, args.batch, args.ctx, args.small, sizes)
     if args.impl == "reference":

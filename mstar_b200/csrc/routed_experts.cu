@@ -162,3 +162,241 @@ MSTAR_API int mstar_experts_by_row(const void* x, const void* w_gate_up, const v
     }
     return launch_status();
 }
+
+// ====================================================================== grouped by expert
+// For many rows (prompt portions) the rows are sorted by expert, and every expert's rows go
+// through its matrices as tiles of a tensor-core GEMM (bfloat16 mma.sync, float sums):
+//   1. experts_sort: counting sort of the rows (token x choice) by expert; the list of row
+//      tiles (expert, first sorted row), one per 64 rows of a group.
+//   2. grouped GEMM, gated: act[p] = silu(w G) * (w U), G and U the products of the gathered
+//      token rows with the expert's gate and up rows (bfloat16 out, sorted order).
+//   3. grouped GEMM, plain: y[p] = act[p] W_down[e]^T (float out, sorted order).
+//   4. experts_combine: out[t] = sum over a token's choices, in the order of the choices,
+//      of (w) y[pos] (+ add[t]).
+// A row's numbers depend on its own inputs only: the position of a row in its tile changes
+// nothing, so the order inside a group need not be stable.
+#include "mma_util.cuh"
+
+#define GG_BM 64
+#define GG_BN 64
+#define GG_BK 32
+#define GG_LD 40          // bf16 elements between rows of a shared tile (80 bytes: no bank conflicts)
+#define GG_THREADS 128
+#define GG_STAGES 3
+
+__global__ void experts_sort_kernel(const int* __restrict__ chosen, int rows, int experts,
+                                    int* __restrict__ order, int* __restrict__ pos,
+                                    int* __restrict__ offsets, int* __restrict__ tile_expert,
+                                    int* __restrict__ tile_first, int* __restrict__ num_tiles) {
+    extern __shared__ int sh[];               // counts[experts], cursor[experts]
+    int* counts = sh;
+    int* cursor = sh + experts;
+    chosen = pdl_after(chosen, pdl_wait());
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
+    for (int r = threadIdx.x; r < rows; r += blockDim.x) atomicAdd(&counts[chosen[r]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, tiles = 0;
+        for (int e = 0; e < experts; ++e) {
+            offsets[e] = at;
+            cursor[e] = at;
+            for (int p = at; p < at + counts[e]; p += GG_BM) {
+                tile_expert[tiles] = e;
+                tile_first[tiles] = p;
+                ++tiles;
+            }
+            at += counts[e];
+        }
+        offsets[experts] = at;
+        *num_tiles = tiles;
+    }
+    __syncthreads();
+    for (int r = threadIdx.x; r < rows; r += blockDim.x) {
+        const int p = atomicAdd(&cursor[chosen[r]], 1);
+        order[p] = r;
+        pos[r] = p;
+    }
+}
+
+// C tile [64 x 64] of one expert's group.  GATED: A rows are x[order[p] / top], B rows are
+// the expert's gate rows n0.. and up rows ff + n0..; out = silu(w G) * (w U) as bfloat16.
+// Plain: A rows are act[p], B rows the expert's down rows n0..; out float.
+template <bool GATED>
+__global__ void __launch_bounds__(GG_THREADS)
+grouped_gemm_kernel(const bf16* __restrict__ a_src, const bf16* __restrict__ w, void* __restrict__ out,
+                    const int* __restrict__ order, const float* __restrict__ weight,
+                    const int* __restrict__ offsets, const int* __restrict__ tile_expert,
+                    const int* __restrict__ tile_first, const int* __restrict__ num_tiles,
+                    int N, int K, int top, int scale_input) {
+    constexpr int BROWS = GATED ? 2 * GG_BN : GG_BN;
+    __shared__ __align__(16) bf16 As[GG_STAGES][GG_BM * GG_LD];
+    __shared__ __align__(16) bf16 Bs[GG_STAGES][BROWS * GG_LD];
+    __shared__ int src_row[GG_BM];
+
+    const unsigned long long waited = pdl_wait();
+    a_src = pdl_after(a_src, waited);
+    order = pdl_after(order, waited);
+    num_tiles = pdl_after(num_tiles, waited);
+    if ((int)blockIdx.y >= *num_tiles) return;
+    const int e = tile_expert[blockIdx.y], p0 = tile_first[blockIdx.y];
+    const int p_end = offsets[e + 1];
+    const int n0 = blockIdx.x * GG_BN;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
+
+    if (tid < GG_BM) {
+        const int p = p0 + tid;
+        src_row[tid] = p < p_end ? (GATED ? order[p] / top : p) : -1;
+    }
+    __syncthreads();
+    const bf16* wbase = w + (size_t)e * (GATED ? 2 : 1) * N * K;
+
+    auto load_stage = [&](int stage, int k0) {
+        // A: 64 rows x 4 chunks of 8
+        for (int c = tid; c < GG_BM * 4; c += GG_THREADS) {
+            const int r = c >> 2, kc = (c & 3) * 8;
+            const int src = src_row[r];
+            const bool ok = src >= 0 && k0 + kc < K;
+            const bf16* g = a_src + (ok ? (size_t)src * K + k0 + kc : 0);
+            cp_async_16(smem_u32(&As[stage][r * GG_LD + kc]), g, ok ? 16 : 0);
+        }
+        for (int c = tid; c < BROWS * 4; c += GG_THREADS) {
+            const int r = c >> 2, kc = (c & 3) * 8;
+            const int n = n0 + (r % GG_BN);
+            const bool ok = n < N && k0 + kc < K;
+            const size_t wrow = (GATED && r >= GG_BN) ? (size_t)N + n : (size_t)n;
+            const bf16* g = wbase + (ok ? wrow * K + k0 + kc : 0);
+            cp_async_16(smem_u32(&Bs[stage][r * GG_LD + kc]), g, ok ? 16 : 0);
+        }
+    };
+
+    float acc[GATED ? 2 : 1][2][4][4];
+#pragma unroll
+    for (int s = 0; s < (GATED ? 2 : 1); ++s)
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int q = 0; q < 4; ++q) acc[s][i][j][q] = 0.f;
+
+    const int k_tiles = (K + GG_BK - 1) / GG_BK;
+#pragma unroll
+    for (int s = 0; s < GG_STAGES - 1; ++s) {
+        if (s < k_tiles) load_stage(s, s * GG_BK);
+        cp_async_commit();
+    }
+    for (int kt = 0; kt < k_tiles; ++kt) {
+        cp_async_wait<GG_STAGES - 2>();
+        __syncthreads();
+        const int next = kt + GG_STAGES - 1;
+        if (next < k_tiles) load_stage(next % GG_STAGES, next * GG_BK);
+        cp_async_commit();
+        const bf16* At = As[kt % GG_STAGES];
+        const bf16* Bt = Bs[kt % GG_STAGES];
+#pragma unroll
+        for (int kk = 0; kk < GG_BK; kk += 16) {
+            uint32_t af[2][4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+                ldmatrix_x4(af[i], smem_u32(&At[(wm + i * 16 + (lane & 15)) * GG_LD + kk + (lane >> 4) * 8]));
+#pragma unroll
+            for (int s = 0; s < (GATED ? 2 : 1); ++s) {
+#pragma unroll
+                for (int jp = 0; jp < 2; ++jp) {
+                    uint32_t bfr[4];
+                    const int brow = s * GG_BN + wn + jp * 16 + (lane & 7) + (lane >> 4) * 8;
+                    ldmatrix_x4(bfr, smem_u32(&Bt[brow * GG_LD + kk + ((lane >> 3) & 1) * 8]));
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        mma_bf16_16816(acc[s][i][jp * 2], af[i], bfr[0], bfr[1]);
+                        mma_bf16_16816(acc[s][i][jp * 2 + 1], af[i], bfr[2], bfr[3]);
+                    }
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+
+    const int g = lane >> 2, t4 = lane & 3;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = wm + i * 16 + g + half * 8;
+            const int p = p0 + r;
+            if (p >= p_end) continue;
+            float wgt = 1.f;
+            if (GATED && scale_input) wgt = weight[order[p]];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int n = n0 + wn + j * 8 + 2 * t4;
+                if (n >= N) continue;
+                if (GATED) {
+                    const float g0 = acc[0][i][j][half * 2] * wgt, g1 = acc[0][i][j][half * 2 + 1] * wgt;
+                    const float u0 = acc[GATED ? 1 : 0][i][j][half * 2] * wgt;
+                    const float u1 = acc[GATED ? 1 : 0][i][j][half * 2 + 1] * wgt;
+                    bf16* o = (bf16*)out + (size_t)p * N + n;
+                    o[0] = __float2bfloat16_rn(g0 / (1.f + expf(-g0)) * u0);
+                    if (n + 1 < N) o[1] = __float2bfloat16_rn(g1 / (1.f + expf(-g1)) * u1);
+                } else {
+                    float* o = (float*)out + (size_t)p * N + n;
+                    o[0] = acc[0][i][j][half * 2];
+                    if (n + 1 < N) o[1] = acc[0][i][j][half * 2 + 1];
+                }
+            }
+        }
+    }
+}
+
+template <typename A>
+__global__ void experts_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos,
+                                       const float* __restrict__ weight, const A* __restrict__ add,
+                                       A* __restrict__ out, int width, int top, int scale_input) {
+    const unsigned long long waited = pdl_wait();
+    y = pdl_after(y, waited);
+    pos = pdl_after(pos, waited);
+    add = pdl_after(add, waited);
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float total = 0.f;
+        for (int k = 0; k < top; ++k) {
+            const float v = y[(size_t)pos[(size_t)t * top + k] * width + c];
+            total += scale_input ? v : v * weight[(size_t)t * top + k];
+        }
+        if (add != nullptr) total += to_float(add[(size_t)t * width + c]);
+        out[(size_t)t * width + c] = from_float<A>(total);
+    }
+}
+
+// bfloat16 only.  `ints`: scratch of 2 * rows + experts + 2 + 2 * (rows / 64 + experts) ints;
+// `act`: bfloat16 [rows, ff]; `y`: float [rows, width] (rows = tokens * top).  Returns 0, a CUDA
+// error code, or -1 when the shape is refused (width or ff no multiple of 8, over 1024 experts).
+MSTAR_API int mstar_experts_grouped(const void* x, const void* w_gate_up, const void* w_down,
+                                    const int* chosen, const float* weight, int* ints, void* act,
+                                    float* y, const void* add, void* out, int tokens, int width,
+                                    int ff, int top, int experts, int scale_input, void* stream) {
+    if (tokens <= 0) return 0;
+    if (width % 8 != 0 || ff % 8 != 0 || experts <= 0 || experts > 1024 || top <= 0) return -1;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int rows = tokens * top;
+    const int max_tiles = rows / GG_BM + experts;
+    int* order = ints;
+    int* pos = order + rows;
+    int* offsets = pos + rows;
+    int* num_tiles = offsets + experts + 1;
+    int* tile_expert = num_tiles + 1;
+    int* tile_first = tile_expert + max_tiles;
+    mstar_launch(experts_sort_kernel, dim3(1), dim3(1024), sizeof(int) * 2 * experts, s, chosen, rows,
+                 experts, order, pos, offsets, tile_expert, tile_first, num_tiles);
+    mstar_launch((grouped_gemm_kernel<true>), dim3((ff + GG_BN - 1) / GG_BN, max_tiles), dim3(GG_THREADS),
+                 0, s, (const bf16*)x, (const bf16*)w_gate_up, act, order, weight, offsets, tile_expert,
+                 tile_first, num_tiles, ff, width, top, scale_input);
+    mstar_launch((grouped_gemm_kernel<false>), dim3((width + GG_BN - 1) / GG_BN, max_tiles),
+                 dim3(GG_THREADS), 0, s, (const bf16*)act, (const bf16*)w_down, (void*)y, order, weight,
+                 offsets, tile_expert, tile_first, num_tiles, width, ff, top, scale_input);
+    mstar_launch((experts_combine_kernel<bf16>), dim3(tokens), dim3(256), 0, s, (const float*)y, pos,
+                 weight, (const bf16*)add, (bf16*)out, width, top, scale_input);
+    return launch_status();
+}

@@ -906,3 +906,52 @@ def experts_by_row(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tenso
     check(code, "experts_by_row")
     lib.add_launches(1)                       # two kernels behind one call
     return out
+
+
+# Rows (tokens x choices) from which on the experts' rows are sorted by expert and run as
+# tiles of a tensor-core GEMM; below, every row streams its experts' matrices by itself.
+GROUPED_EXPERT_ROWS = 64
+
+
+def experts_grouped(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, chosen, weight,
+                    experts: int, ff: int, scale_input: bool, add=None) -> torch.Tensor:
+    """The same sums as ``experts_by_row`` for many bfloat16 rows: rows sorted by expert on
+    the device, each expert's rows through its matrices as 64-row tiles on the tensor cores
+    (float sums), a token's choices added up in their order.  Nothing is read by the host."""
+    _need_cuda(x, w_gate_up, w_down, chosen, weight, add)
+    tokens, width = x.shape
+    top = chosen.shape[1]
+    assert x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16
+    assert w_down.dtype == torch.bfloat16 and x.is_contiguous()
+    assert w_gate_up.is_contiguous() and w_down.is_contiguous()
+    assert tuple(w_gate_up.shape) == (experts * 2 * ff, width)
+    assert tuple(w_down.shape) == (experts * width, ff)
+    assert add is None or (add.shape == x.shape and add.is_contiguous() and add.dtype == x.dtype)
+    rows = tokens * top
+    ints = torch.empty(2 * rows + experts + 2 + 2 * (rows // 64 + experts), dtype=torch.int32,
+                       device=x.device)
+    act = torch.empty((rows, ff), dtype=torch.bfloat16, device=x.device)
+    y = torch.empty((rows, width), dtype=torch.float32, device=x.device)
+    out = torch.empty_like(x)
+    code = lib.get("routed_experts").mstar_experts_grouped(
+        x.data_ptr(), w_gate_up.data_ptr(), w_down.data_ptr(), chosen.data_ptr(),
+        weight.data_ptr(), ints.data_ptr(), act.data_ptr(), y.data_ptr(), _ptr(add),
+        out.data_ptr(), tokens, width, ff, top, experts, int(scale_input), _stream())
+    if code == -1:
+        raise KernelError(f"the grouped expert kernels refuse width={width}, ff={ff}, "
+                          f"experts={experts} (width and ff multiples of 8, at most 1024 experts)")
+    check(code, "experts_grouped")
+    lib.add_launches(3)                       # four kernels behind one call
+    return out
+
+
+def routed_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, chosen, weight,
+                   experts: int, ff: int, scale_input: bool, add=None) -> torch.Tensor:
+    """sum over a token's chosen experts of down(silu(gate u) * up u) (+ ``add``): sorted by
+    expert on the tensor cores from ``GROUPED_EXPERT_ROWS`` bfloat16 rows on
+    (MSTAR_EXPERTS=by_row: never), row by row below and in float32."""
+    rows = x.shape[0] * chosen.shape[1]
+    if (x.dtype == torch.bfloat16 and rows >= GROUPED_EXPERT_ROWS and x.shape[1] % 8 == 0
+            and ff % 8 == 0 and experts <= 1024 and os.environ.get("MSTAR_EXPERTS") != "by_row"):
+        return experts_grouped(x, w_gate_up, w_down, chosen, weight, experts, ff, scale_input, add)
+    return experts_by_row(x, w_gate_up, w_down, chosen, weight, ff, scale_input, add)

@@ -46,6 +46,8 @@ _SIGNATURES = {
         "mstar_route_topk": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
         "mstar_experts_by_row": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
                                  _vp],
+        "mstar_experts_grouped": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
+                                  _i, _i, _vp],
     },
     "attention_generic": {
         "mstar_paged_attention_generic": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i,

@@ -4,7 +4,9 @@ feed-forwards per token; an optional shared one runs for every token and is adde
 The router's logits are a product with float output; a kernel turns them into the chosen
 experts and their weights (sigmoid or softmax scores, renormalised or not).  The shared
 expert is the dense gated feed-forward's path (one fused gate/up product, one down
-product); the routed experts' kernels add its output while they write theirs.
+product); the routed experts' kernels add its output while they write theirs.  A few rows
+(decoded tokens) each stream the matrices of their experts; many rows (prompt portions)
+are sorted by expert on the device and run as tiles on the tensor cores.
 """
 from __future__ import annotations
 
@@ -55,8 +57,8 @@ class RoutedExperts:
         if self.shared_gate_up is not None:
             shared = ops.linear(ops.gated_up(x, self.shared_gate_up, static_weights=True),
                                 self.shared_down, static_weights=True)
-        return ops.experts_by_row(x, self.gate_up, self.down, chosen, weight, s.expert_size,
-                                  s.scale_input, add=shared)
+        return ops.routed_experts(x, self.gate_up, self.down, chosen, weight, s.num_experts,
+                                  s.expert_size, s.scale_input, add=shared)
 
 
 register_part("ffn", "routed_experts", RoutedExperts)

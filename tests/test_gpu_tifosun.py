@@ -382,3 +382,38 @@ def test_greedy_generation_through_the_entry_point(mixed_model, dtype, tmp_path)
             far_off += tok != best and margin >= 0.25
             logits = plain.forward([tok])[-1]
     assert far_off <= len(prompts) * n_new // 20, far_off
+
+
+@pytest.mark.parametrize("experts,top,width,ff,tokens,on_input",
+                         [(5, 2, 96, 24, 200, True), (12, 1, 64, 40, 64, True),
+                          (7, 3, 136, 72, 333, False), (3, 3, 96, 8, 70, True)])
+def test_experts_sorted_by_expert_agree_with_rows_alone(experts, top, width, ff, tokens, on_input):
+    """Many bfloat16 rows go through the experts sorted by expert, as tiles on the tensor
+    cores; a few rows each stream their experts' matrices.  Both against the plain sums, and
+    against each other: groups that end inside a tile, an expert nobody chose, widths and
+    expert sizes that are no multiple of a tile."""
+    from mstar_b200 import ops
+
+    g = torch.Generator().manual_seed(experts)
+    x = torch.randn(tokens, width, generator=g).to(torch.bfloat16)
+    w_gu = (torch.randn(experts * 2 * ff, width, generator=g) / width ** 0.5).to(torch.bfloat16)
+    w_dn = (torch.randn(experts * width, ff, generator=g) / ff ** 0.5).to(torch.bfloat16)
+    add = torch.randn(tokens, width, generator=g).to(torch.bfloat16)
+    z = torch.randn(tokens, experts, generator=g)
+    z[:, 1] = -30.0                                  # nobody chooses expert 1 (unless all are)
+    chosen, weight = ops.route_topk(z.to(DEV), top)
+    want = add.double().clone()
+    for t in range(tokens):
+        for k in range(top):
+            e, a = int(chosen[t, k]), float(weight[t, k])
+            gate, up = w_gu[e * 2 * ff:e * 2 * ff + ff].double(), w_gu[e * 2 * ff + ff:(e + 1) * 2 * ff].double()
+            down = w_dn[e * width:(e + 1) * width].double()
+            xt = x[t:t + 1].double()
+            want[t] += (P.gated_ffn(a * xt, gate, up, down)[0] if on_input
+                        else a * P.gated_ffn(xt, gate, up, down)[0])
+    args = (x.to(DEV), w_gu.to(DEV), w_dn.to(DEV), chosen, weight)
+    grouped = ops.experts_grouped(*args, experts, ff, on_input, add=add.to(DEV))
+    by_row = ops.experts_by_row(*args, ff, on_input, add=add.to(DEV))
+    close(grouped, want, "bfloat16", "sorted by expert", bf16=2e-2)
+    close(by_row, want, "bfloat16", "row by row", bf16=2e-2)
+    assert ops.routed_experts(*args, experts, ff, on_input, add=add.to(DEV)).equal(grouped)
