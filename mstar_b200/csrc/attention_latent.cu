@@ -12,7 +12,9 @@
 //
 // Every head reads the same rows, so a block takes one token and a group of heads and
 // streams the rows through shared memory once, 32 keys at a time, anchored at the token's
-// own first visible key: what a token computes does not depend on the batch it is in.
+// own first visible key.  With few tokens in a step the keys of a token are shared among
+// several blocks (tile i of the token goes to block i modulo the number of splits) whose
+// partial sums a second kernel merges in the order of the splits.
 //
 // The first kernel fills the cache: it normalises the latent part of the down-projection
 // (RMS, plain weight), rotates the shared key part and the rotated part of every query head
@@ -27,25 +29,63 @@ struct LatentArgs {
     int heads, group, rank, rot, page_size, bt_stride, window;
     int ldq;      // elements between tokens of the rotated query part
     int q_head;   // elements between heads of the rotated query part
+    int splits;   // blocks that share a token's keys (tile i goes to block i % splits)
     float scale;
 };
 
-template <typename A>
+// A row of D cache elements into floats in shared memory; 16-byte loads where the row allows.
+__device__ __forceinline__ void latent_row_to_smem(const bf16* src, float* dst, int D, int lane_id,
+                                                   int lanes, bool vec) {
+    if (vec) {
+        for (int c = lane_id; c < (D >> 3); c += lanes) {
+            float v[8];
+            load8(src + 8 * c, v);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dst[8 * c + i] = v[i];
+        }
+    } else {
+        for (int d = lane_id; d < D; d += lanes) dst[d] = to_float(src[d]);
+    }
+}
+__device__ __forceinline__ void latent_row_to_smem(const float* src, float* dst, int D, int lane_id,
+                                                   int lanes, bool vec) {
+    if (vec) {
+        for (int c = lane_id; c < (D >> 2); c += lanes) {
+            const float4 v = reinterpret_cast<const float4*>(src)[c];
+            dst[4 * c] = v.x; dst[4 * c + 1] = v.y; dst[4 * c + 2] = v.z; dst[4 * c + 3] = v.w;
+        }
+    } else {
+        for (int d = lane_id; d < D; d += lanes) dst[d] = src[d];
+    }
+}
+
+// out: [tokens, heads, rank] when splits == 1 (normalised), else the partial sums of a split
+// go to part_acc [tokens, heads, splits, rank] with part_ml [tokens, heads, splits, 2] =
+// (maximum, sum of exponentials), and the merge kernel finishes.
+//
+// GP heads a block (4, 8 or 16; fewer are padded with zero queries), CPT = 32 / GP output
+// columns a thread: a thread keeps GP x CPT sums in registers.  Queries and probabilities lie
+// in shared memory with the heads innermost, so that one 16-byte load brings a key's or a
+// feature's values for four heads: a score step is 2 loads for 4 multiply-adds, an output
+// step GP / 4 + CPT loads for 32.
+template <typename A, int GP>
 __global__ void __launch_bounds__(LAT_THREADS)
 latent_attention_kernel(const float* __restrict__ q_abs, const A* __restrict__ q_rot,
-                        float* __restrict__ out, const A* __restrict__ cache,
+                        float* __restrict__ out, float* __restrict__ part_acc,
+                        float* __restrict__ part_ml, const A* __restrict__ cache,
                         const int* __restrict__ block_table, const int* __restrict__ token_req,
                         const int* __restrict__ cache_pos, LatentArgs a) {
-    extern __shared__ float smem[];
-    const int t = blockIdx.x, h0 = blockIdx.y * a.group;
+    constexpr int CPT = LAT_MAX_ACC / GP;
+    extern __shared__ __align__(16) float smem[];
+    const int t = blockIdx.x, h0 = blockIdx.y * a.group, split = blockIdx.z;
     const int G = min(a.group, a.heads - h0);
     const int D = a.rank + a.rot, ldk = D + 1;
-    float* qs = smem;                         // [group][D]
-    float* tile = qs + a.group * D;           // [TILE][D+1]
-    float* sc = tile + LAT_TILE * ldk;        // [group][TILE]
-    float* m_s = sc + a.group * LAT_TILE;     // [group]
-    float* l_s = m_s + a.group;
-    float* alpha_s = l_s + a.group;
+    float* qs = smem;                         // [D][GP]
+    float* sc = qs + D * GP;                  // [TILE][GP]
+    float* m_s = sc + LAT_TILE * GP;          // [GP]
+    float* l_s = m_s + GP;
+    float* alpha_s = l_s + GP;
+    float* tile = alpha_s + GP;               // [TILE][D+1]
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const unsigned long long waited = pdl_wait();
@@ -56,55 +96,73 @@ latent_attention_kernel(const float* __restrict__ q_abs, const A* __restrict__ q
     const int hi = cache_pos[t] + 1;
     const int lo = (a.window > 0 && hi > a.window) ? hi - a.window : 0;
     const int* bt = block_table + (size_t)token_req[t] * a.bt_stride;
+    // rows start at multiples of D elements: 16-byte loads need D to be a multiple of 8 (4)
+    const bool vec = (D % (16 / (int)sizeof(A)) == 0) && (((uintptr_t)cache & 15) == 0);
 
-    for (int i = tid; i < G * D; i += LAT_THREADS) {
+    for (int i = tid; i < GP * D; i += LAT_THREADS) {
         const int g = i / D, d = i - g * D;
-        qs[i] = d < a.rank ? q_abs[((size_t)t * a.heads + h0 + g) * a.rank + d]
+        float v = 0.f;
+        if (g < G)
+            v = d < a.rank ? q_abs[((size_t)t * a.heads + h0 + g) * a.rank + d]
                            : to_float(q_rot[(size_t)t * a.ldq + (size_t)(h0 + g) * a.q_head + (d - a.rank)]);
+        qs[d * GP + g] = v;
     }
-    for (int i = tid; i < G; i += LAT_THREADS) {
+    for (int i = tid; i < GP; i += LAT_THREADS) {
         m_s[i] = -INFINITY;
         l_s[i] = 0.f;
     }
-    float acc[LAT_MAX_ACC];
+    float acc[CPT][GP];
 #pragma unroll
-    for (int k = 0; k < LAT_MAX_ACC; ++k) acc[k] = 0.f;
-    const int n_out = G * a.rank;
+    for (int c = 0; c < CPT; ++c)
+#pragma unroll
+        for (int g = 0; g < GP; ++g) acc[c][g] = 0.f;
     __syncthreads();
 
-    for (int base = lo; base < hi; base += LAT_TILE) {
-        for (int idx = tid; idx < LAT_TILE * D; idx += LAT_THREADS) {
-            const int j = idx / D, d = idx - j * D;
+    for (int base = lo + split * LAT_TILE; base < hi; base += a.splits * LAT_TILE) {
+        // a quarter warp per row: 8 lanes stream the row with wide loads.  (Bringing the rows by
+        // asynchronous copies through a staging buffer was tried: the buffer leaves one block
+        // per SM instead of two, and the kernel took 1.7 times as long.)
+        for (int j = tid >> 3; j < LAT_TILE; j += LAT_THREADS >> 3) {
             const int key = base + j;
-            float v = 0.f;
+            float* dst = tile + j * ldk;
             if (key < hi) {
                 const int page = bt[key / a.page_size];
-                const int slot = key % a.page_size;
-                v = to_float(cache[((size_t)page * a.page_size + slot) * D + d]);
+                const A* src = cache + ((size_t)page * a.page_size + key % a.page_size) * D;
+                latent_row_to_smem(src, dst, D, tid & 7, 8, vec);
+            } else {
+                for (int d = tid & 7; d < D; d += 8) dst[d] = 0.f;
             }
-            tile[j * ldk + d] = v;
         }
         __syncthreads();
-        for (int idx = tid; idx < G * LAT_TILE; idx += LAT_THREADS) {
-            const int g = idx / LAT_TILE, j = idx - g * LAT_TILE;
-            float s = -INFINITY;
-            if (base + j < hi) {
-                const float* qv = qs + g * D;
-                const float* kv = tile + j * ldk;
-                float dot = 0.f;
-                for (int d = 0; d < D; ++d) dot = fmaf(qv[d], kv[d], dot);
-                s = dot * a.scale;
+        // scores: a thread takes one key and four heads
+        for (int quad = warp; quad < GP / 4; quad += LAT_THREADS / 32) {
+            const float* kv = tile + lane * ldk;
+            float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll 4
+            for (int d = 0; d < D; ++d) {
+                const float4 q4 = *reinterpret_cast<const float4*>(qs + d * GP + 4 * quad);
+                const float k = kv[d];
+                s0 = fmaf(q4.x, k, s0);
+                s1 = fmaf(q4.y, k, s1);
+                s2 = fmaf(q4.z, k, s2);
+                s3 = fmaf(q4.w, k, s3);
             }
-            sc[idx] = s;
+            const bool seen = base + lane < hi;
+            float4 r;
+            r.x = seen ? s0 * a.scale : -INFINITY;
+            r.y = seen ? s1 * a.scale : -INFINITY;
+            r.z = seen ? s2 * a.scale : -INFINITY;
+            r.w = seen ? s3 * a.scale : -INFINITY;
+            *reinterpret_cast<float4*>(sc + lane * GP + 4 * quad) = r;
         }
         __syncthreads();
-        for (int g = warp; g < G; g += LAT_THREADS / 32) {
-            const float s = sc[g * LAT_TILE + lane];
+        for (int g = warp; g < GP; g += LAT_THREADS / 32) {
+            const float s = sc[lane * GP + g];
             const float m_old = m_s[g];
             const float m_new = fmaxf(m_old, warp_max(s));   // key `base` is always valid
             const float p = expf(s - m_new);
             const float psum = warp_sum(p);
-            sc[g * LAT_TILE + lane] = p;
+            sc[lane * GP + g] = p;
             if (lane == 0) {
                 const float al = expf(m_old - m_new);
                 alpha_s[g] = al;
@@ -113,67 +171,134 @@ latent_attention_kernel(const float* __restrict__ q_abs, const A* __restrict__ q
             }
         }
         __syncthreads();
+        {
+            float al[GP];
 #pragma unroll
-        for (int k = 0; k < LAT_MAX_ACC; ++k) {
-            const int o = tid + k * LAT_THREADS;
-            if (o < n_out) {
-                const int g = o / a.rank, d = o - g * a.rank;
-                const float* p = sc + g * LAT_TILE;
-                float sum = acc[k] * alpha_s[g];
-#pragma unroll 8
-                for (int j = 0; j < LAT_TILE; ++j) sum = fmaf(p[j], tile[j * ldk + d], sum);
-                acc[k] = sum;
+            for (int g = 0; g < GP; ++g) al[g] = alpha_s[g];
+#pragma unroll
+            for (int c = 0; c < CPT; ++c)
+#pragma unroll
+                for (int g = 0; g < GP; ++g) acc[c][g] *= al[g];
+        }
+        for (int j = 0; j < LAT_TILE; ++j) {
+            float p[GP];
+#pragma unroll
+            for (int q4 = 0; q4 < GP / 4; ++q4) {
+                const float4 v = *reinterpret_cast<const float4*>(sc + j * GP + 4 * q4);
+                p[4 * q4] = v.x; p[4 * q4 + 1] = v.y; p[4 * q4 + 2] = v.z; p[4 * q4 + 3] = v.w;
+            }
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) {
+                const int d = tid + c * LAT_THREADS;
+                const float v = d < a.rank ? tile[j * ldk + d] : 0.f;
+#pragma unroll
+                for (int g = 0; g < GP; ++g) acc[c][g] = fmaf(p[g], v, acc[c][g]);
             }
         }
         __syncthreads();
     }
 #pragma unroll
-    for (int k = 0; k < LAT_MAX_ACC; ++k) {
-        const int o = tid + k * LAT_THREADS;
-        if (o < n_out) {
-            const int g = o / a.rank, d = o - g * a.rank;
-            out[((size_t)t * a.heads + h0 + g) * a.rank + d] = acc[k] / l_s[g];
+    for (int c = 0; c < CPT; ++c) {
+        const int d = tid + c * LAT_THREADS;
+        if (d >= a.rank) continue;
+#pragma unroll
+        for (int g = 0; g < GP; ++g) {
+            if (g >= G) continue;
+            const size_t th = (size_t)t * a.heads + h0 + g;
+            if (a.splits == 1) {
+                out[th * a.rank + d] = acc[c][g] / l_s[g];
+            } else {
+                part_acc[(th * a.splits + split) * a.rank + d] = acc[c][g];
+                if (d == 0) {
+                    part_ml[(th * a.splits + split) * 2] = m_s[g];
+                    part_ml[(th * a.splits + split) * 2 + 1] = l_s[g];
+                }
+            }
         }
     }
 }
 
-// Returns 0, a CUDA error code, or -1 when the shape is refused (rank > 4096, or a tile of
-// rows that does not fit shared memory).
+// out[t, h, :] = sum_s exp(m_s - M) acc_s / sum_s exp(m_s - M) l_s, in the order of the splits.
+// A split that saw no key has l = 0 and m = -inf and adds nothing.
+__global__ void latent_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                                    float* __restrict__ out, int rank, int splits) {
+    const unsigned long long waited = pdl_wait();
+    part_acc = pdl_after(part_acc, waited);
+    part_ml = pdl_after(part_ml, waited);
+    const size_t th = blockIdx.x;
+    float M = -INFINITY;
+    for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[(th * splits + s) * 2]);
+    float L = 0.f;
+    for (int s = 0; s < splits; ++s) {
+        const float m = part_ml[(th * splits + s) * 2];
+        if (m > -INFINITY) L += expf(m - M) * part_ml[(th * splits + s) * 2 + 1];
+    }
+    for (int d = threadIdx.x; d < rank; d += blockDim.x) {
+        float sum = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float m = part_ml[(th * splits + s) * 2];
+            if (m > -INFINITY) sum = fmaf(expf(m - M), part_acc[(th * splits + s) * rank + d], sum);
+        }
+        out[th * rank + d] = sum / L;
+    }
+}
+
+template <typename A, int GP>
+static int launch_latent(const float* q_abs, const void* q_rot, float* out, float* part_acc,
+                         float* part_ml, const void* cache, const int* block_table,
+                         const int* token_req, const int* cache_pos, const LatentArgs& a, dim3 grid,
+                         size_t smem, cudaStream_t s) {
+    static size_t configured = 0;             // largest dynamic shared memory set so far
+    if (smem > 48 * 1024 && smem > configured) {
+        cudaFuncSetAttribute(latent_attention_kernel<A, GP>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        configured = smem;
+    }
+    mstar_launch((latent_attention_kernel<A, GP>), grid, dim3(LAT_THREADS), smem, s, q_abs,
+                 (const A*)q_rot, out, part_acc, part_ml, (const A*)cache, block_table, token_req,
+                 cache_pos, a);
+    return 0;
+}
+
+// `group` heads a block (0: as many as fit), `splits` > 1 shares a token's keys among that many
+// blocks (`scratch`: float [tokens * heads * splits * (rank + 2)]).  Returns 0, a CUDA error
+// code, or -1 when the shape is refused (rank > 1024, or a tile of rows that does not fit
+// shared memory).
 MSTAR_API int mstar_latent_attention(const float* q_abs, const void* q_rot, int ldq, int q_head,
                                      float* out, const void* cache, const int* block_table,
                                      int bt_stride, const int* token_req, const int* cache_pos,
                                      int num_tokens, int heads, int rank, int rot, int page_size,
-                                     int window, float scale, int act_dtype, void* stream) {
+                                     int window, float scale, int act_dtype, int group, int splits,
+                                     float* scratch, void* stream) {
     if (num_tokens <= 0) return 0;
-    if (heads <= 0 || rank <= 0 || rot < 0 || rank > LAT_MAX_ACC * LAT_THREADS) return -1;
-    int group = (LAT_MAX_ACC * LAT_THREADS) / rank;
+    if (heads <= 0 || rank <= 0 || rot < 0 || rank > 8 * LAT_THREADS) return -1;
+    // heads a block: a thread has 32 sums for GP heads x (rank / 128) columns
+    const int most = rank <= 2 * LAT_THREADS ? 16 : (rank <= 4 * LAT_THREADS ? 8 : 4);
+    if (group <= 0 || group > most) group = most;
     if (group > heads) group = heads;
-    if (group > 16) group = 16;
+    const int gp = group <= 4 ? 4 : (group <= 8 ? 8 : 16);
+    if (splits < 1) splits = 1;
+    if (splits > 1 && scratch == nullptr) return -1;
     const int D = rank + rot;
-    const size_t smem = sizeof(float) * ((size_t)group * D + (size_t)LAT_TILE * (D + 1) +
-                                         (size_t)group * LAT_TILE + 3 * (size_t)group);
+    const size_t smem = sizeof(float) * ((size_t)gp * D + (size_t)LAT_TILE * (D + 1) +
+                                   (size_t)gp * LAT_TILE + 3 * (size_t)gp);
     if (smem > 200 * 1024) return -1;
     cudaStream_t s = (cudaStream_t)stream;
-    LatentArgs a{heads, group, rank, rot, page_size, bt_stride, window, ldq, q_head, scale};
-    dim3 grid(num_tokens, (heads + group - 1) / group);
-    static size_t configured_f32 = 0, configured_bf16 = 0;
+    LatentArgs a{heads, group, rank, rot, page_size, bt_stride, window, ldq, q_head, splits, scale};
+    dim3 grid(num_tokens, (heads + group - 1) / group, splits);
+    float* part_acc = scratch;
+    float* part_ml = scratch == nullptr ? nullptr : scratch + (size_t)num_tokens * heads * splits * rank;
+#define GO(A, GP) launch_latent<A, GP>(q_abs, q_rot, out, part_acc, part_ml, cache, block_table, \
+                                       token_req, cache_pos, a, grid, smem, s)
     if (act_dtype == MSTAR_F32) {
-        if (smem > 48 * 1024 && smem > configured_f32) {
-            cudaFuncSetAttribute(latent_attention_kernel<float>,
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            configured_f32 = smem;
-        }
-        mstar_launch((latent_attention_kernel<float>), grid, dim3(LAT_THREADS), smem, s, q_abs,
-                     (const float*)q_rot, out, (const float*)cache, block_table, token_req, cache_pos, a);
+        if (gp == 4) GO(float, 4); else if (gp == 8) GO(float, 8); else GO(float, 16);
     } else {
-        if (smem > 48 * 1024 && smem > configured_bf16) {
-            cudaFuncSetAttribute(latent_attention_kernel<bf16>,
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            configured_bf16 = smem;
-        }
-        mstar_launch((latent_attention_kernel<bf16>), grid, dim3(LAT_THREADS), smem, s, q_abs,
-                     (const bf16*)q_rot, out, (const bf16*)cache, block_table, token_req, cache_pos, a);
+        if (gp == 4) GO(bf16, 4); else if (gp == 8) GO(bf16, 8); else GO(bf16, 16);
     }
+#undef GO
+    if (splits > 1)
+        mstar_launch(latent_merge_kernel, dim3(num_tokens * heads), dim3(128), 0, s,
+                     (const float*)part_acc, (const float*)part_ml, out, rank, splits);
     return launch_status();
 }
 

@@ -12,10 +12,11 @@
 // recurrence is float: gates, decays, the state and the sums; q, k and v are read in the
 // activation type as their products left them.
 //
-// The scan walks a sequence token by token.  A block owns 32 value columns of one head of one
-// batch entry; a column's `dim` state rows are spread over 8 lanes (row d on lane d % 8), so a
-// step costs dim / 8 multiply-adds per thread and three shuffles, and a step's q, k, v and
-// gates are staged in shared memory 16 tokens at a time.  The arithmetic of a token does not
+// The scan walks a sequence token by token.  A block owns 32 (or 8) value columns of one head of
+// one batch entry; a column's `dim` state rows are spread over 8 lanes (row d on lane d % 8), so a
+// step costs dim / 8 multiply-adds per thread and three shuffles; q, k, v and the gates come
+// through shared memory 16 tokens at a time, the next 16 copied (cp.async) while these are
+// walked.  The arithmetic of a token does not
 // depend on how the sequence was cut into steps or on what else is in the batch.
 //
 // State slot layout (floats): S^T [heads][vdim][dim], then n [heads][dim], then m [heads].
@@ -23,10 +24,8 @@
 // The second kernel finishes the cell: each head's output is divided by its root mean
 // square, scaled by a weight and gated by sigmoid(g).
 #include "common.cuh"
+#include "mma_util.cuh"
 
-#define MM_COLS 32
-#define MM_LANES 8
-#define MM_THREADS (MM_COLS * MM_LANES)
 #define MM_CHUNK 16
 
 struct MemArgs {
@@ -43,22 +42,34 @@ __device__ __forceinline__ float log_sigmoid(float x) {
     return fminf(x, 0.f) - log1pf(expf(-fabsf(x)));
 }
 
-template <typename A, int R>
-__global__ void __launch_bounds__(MM_THREADS)
+// Copies `n` consecutive elements (n a multiple of the 16-byte vector) global -> shared.
+template <typename A>
+__device__ __forceinline__ void stage_vec(A* dst, const A* src, int n, int first, int step) {
+    constexpr int V = 16 / (int)sizeof(A);
+    for (int c = first; c < n / V; c += step) cp_async_16(smem_u32(dst + c * V), src + c * V, 16);
+}
+
+template <typename A, int R, int MM_COLS, int MM_LANES>
+__global__ void __launch_bounds__(MM_COLS * MM_LANES)
 matrix_memory_scan_kernel(const A* __restrict__ qkv, const float* __restrict__ gates,
                           const float* __restrict__ bias, const int* __restrict__ qo_indptr,
                           const int* __restrict__ slots, float* __restrict__ state,
                           float* __restrict__ out, MemArgs a) {
-    extern __shared__ float smem[];
-    float* q_s = smem;                         // [CHUNK][dim]
-    float* k_s = q_s + MM_CHUNK * a.dim;       // [CHUNK][dim]
-    float* v_s = k_s + MM_CHUNK * a.dim;       // [CHUNK][COLS]
-    float* i_s = v_s + MM_CHUNK * MM_COLS;     // [CHUNK]
-    float* f_s = i_s + MM_CHUNK;               // [CHUNK]
+    constexpr int MM_THREADS = MM_COLS * MM_LANES;
+    constexpr int V = 16 / (int)sizeof(A);
+    // two stages of a chunk's q, k (this head) and v (this block's columns) as they are in
+    // memory, and of its gates: the next chunk is copied while this one is walked
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    A* q_s = reinterpret_cast<A*>(smem_raw);              // [2][CHUNK][dim]
+    A* k_s = q_s + 2 * MM_CHUNK * a.dim;                  // [2][CHUNK][dim]
+    A* v_s = k_s + 2 * MM_CHUNK * a.dim;                  // [2][CHUNK][COLS]
+    float* i_s = reinterpret_cast<float*>(v_s + 2 * MM_CHUNK * MM_COLS);   // [2][CHUNK]
+    float* f_s = i_s + 2 * MM_CHUNK;                      // [2][CHUNK]
 
     const int entry = blockIdx.z, head = blockIdx.y;
     const int tid = threadIdx.x, lane = tid % MM_LANES, colb = tid / MM_LANES;
-    const int col = blockIdx.x * MM_COLS + colb;
+    const int col0 = blockIdx.x * MM_COLS;
+    const int col = col0 + colb;
     const bool col_ok = col < a.vdim;
     const int t0 = qo_indptr[entry], t1 = qo_indptr[entry + 1];
     // the state is an earlier step's, but the slot may have been zeroed just now: everything
@@ -72,6 +83,52 @@ matrix_memory_scan_kernel(const A* __restrict__ qkv, const float* __restrict__ g
     float* n_g = slot + (size_t)a.heads * a.vdim * a.dim + (size_t)head * a.dim;
     float* m_g = n_g + (size_t)a.heads * a.dim - (size_t)head * a.dim + head;
 
+    // 16-byte copies where rows and columns start on 16-byte boundaries, else element by element
+    const bool base_ok = ((uintptr_t)qkv & 15) == 0 && a.ld % V == 0;
+    const bool qk_vec = base_ok && a.dim % V == 0 && a.k_off % V == 0;
+    const bool v_vec = base_ok && (a.v_off + head * a.vdim + col0) % V == 0 && col0 + MM_COLS <= a.vdim;
+
+    auto stage = [&](int buf, int base, int cnt) {
+        A* qd = q_s + buf * MM_CHUNK * a.dim;
+        A* kd = k_s + buf * MM_CHUNK * a.dim;
+        A* vd = v_s + buf * MM_CHUNK * MM_COLS;
+        if (qk_vec) {
+            const int per = a.dim / V;
+            for (int idx = tid; idx < cnt * per; idx += MM_THREADS) {
+                const int t = idx / per, c = idx - t * per;
+                const A* row = qkv + (size_t)(base + t) * a.ld + (size_t)head * a.dim + c * V;
+                cp_async_16(smem_u32(qd + t * a.dim + c * V), row, 16);
+                cp_async_16(smem_u32(kd + t * a.dim + c * V), row + a.k_off, 16);
+            }
+        } else {
+            for (int idx = tid; idx < cnt * a.dim; idx += MM_THREADS) {
+                const int t = idx / a.dim, d = idx - t * a.dim;
+                const A* row = qkv + (size_t)(base + t) * a.ld + (size_t)head * a.dim + d;
+                qd[idx] = row[0];
+                kd[idx] = row[a.k_off];
+            }
+        }
+        if (v_vec) {
+            constexpr int per = MM_COLS / V;
+            for (int idx = tid; idx < cnt * per; idx += MM_THREADS) {
+                const int t = idx / per, c = idx - t * per;
+                cp_async_16(smem_u32(vd + t * MM_COLS + c * V),
+                            qkv + (size_t)(base + t) * a.ld + a.v_off + (size_t)head * a.vdim + col0 + c * V, 16);
+            }
+        } else {
+            for (int idx = tid; idx < cnt * MM_COLS; idx += MM_THREADS) {
+                const int t = idx / MM_COLS, c = idx - t * MM_COLS;
+                vd[idx] = col0 + c < a.vdim ? qkv[(size_t)(base + t) * a.ld + a.v_off +
+                                                  (size_t)head * a.vdim + col0 + c]
+                                            : from_float<A>(0.f);
+            }
+        }
+    };
+    auto gate_values = [&](float zi, float zf, float& ig, float& fg) {
+        ig = soft_cap(zi + bias[head], a.cap);
+        fg = log_sigmoid(soft_cap(zf + bias[a.heads + head], a.cap));
+    };
+
     float S[R], n[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
@@ -81,42 +138,44 @@ matrix_memory_scan_kernel(const A* __restrict__ qkv, const float* __restrict__ g
     }
     float m = *m_g;
 
-    for (int base = t0; base < t1; base += MM_CHUNK) {
+    const int chunks = (t1 - t0 + MM_CHUNK - 1) / MM_CHUNK;
+    stage(0, t0, min(MM_CHUNK, t1 - t0));
+    cp_async_commit();
+    if (tid < min(MM_CHUNK, t1 - t0)) {
+        const float* g = gates + (size_t)(t0 + tid) * 2 * a.heads;
+        gate_values(g[head], g[a.heads + head], i_s[tid], f_s[tid]);
+    }
+    for (int c = 0; c < chunks; ++c) {
+        const int buf = c & 1, base = t0 + c * MM_CHUNK;
         const int cnt = min(MM_CHUNK, t1 - base);
+        const int cnt_next = min(MM_CHUNK, t1 - base - MM_CHUNK);     // <= 0 after the last chunk
+        if (cnt_next > 0) stage(buf ^ 1, base + MM_CHUNK, cnt_next);
+        cp_async_commit();
+        float zi = 0.f, zf = 0.f;                      // the next chunk's gates: asked for now,
+        if (tid < cnt_next) {                          // used after this chunk's tokens
+            const float* g = gates + (size_t)(base + MM_CHUNK + tid) * 2 * a.heads;
+            zi = g[head];
+            zf = g[a.heads + head];
+        }
+        cp_async_wait<1>();
         __syncthreads();
-        for (int idx = tid; idx < cnt * a.dim; idx += MM_THREADS) {
-            const int t = idx / a.dim, d = idx - t * a.dim;
-            const A* row = qkv + (size_t)(base + t) * a.ld + (size_t)head * a.dim + d;
-            q_s[t * a.dim + d] = to_float(row[0]) * a.q_scale;
-            k_s[t * a.dim + d] = to_float(row[a.k_off]);
-        }
-        for (int idx = tid; idx < cnt * MM_COLS; idx += MM_THREADS) {
-            const int t = idx / MM_COLS, c = idx - t * MM_COLS;
-            const int gc = blockIdx.x * MM_COLS + c;
-            v_s[idx] = gc < a.vdim ? to_float(qkv[(size_t)(base + t) * a.ld + a.v_off +
-                                                  (size_t)head * a.vdim + gc])
-                                   : 0.f;
-        }
-        if (tid < cnt) {
-            const float* g = gates + (size_t)(base + tid) * 2 * a.heads;
-            i_s[tid] = soft_cap(g[head] + bias[head], a.cap);
-            f_s[tid] = log_sigmoid(soft_cap(g[a.heads + head] + bias[a.heads + head], a.cap));
-        }
-        __syncthreads();
+        const A* kb = k_s + buf * MM_CHUNK * a.dim;
+        const A* qb = q_s + buf * MM_CHUNK * a.dim;
+        const A* vb = v_s + buf * MM_CHUNK * MM_COLS;
         for (int t = 0; t < cnt; ++t) {
-            const float fg = f_s[t], ig = i_s[t];
+            const float fg = f_s[buf * MM_CHUNK + t], ig = i_s[buf * MM_CHUNK + t];
             const float m_new = fmaxf(fg + m, ig);
             const float keep = expf(fg + m - m_new), take = expf(ig - m_new);
             m = m_new;
-            const float tv = take * v_s[t * MM_COLS + colb];
-            const float* kq = k_s + t * a.dim;
-            const float* qq = q_s + t * a.dim;
+            const float tv = take * to_float(vb[t * MM_COLS + colb]);
+            const A* kq = kb + t * a.dim;
+            const A* qq = qb + t * a.dim;
             float num = 0.f, nq = 0.f;
 #pragma unroll
             for (int r = 0; r < R; ++r) {
                 const int d = lane + MM_LANES * r;
                 if (d < a.dim) {
-                    const float kd = kq[d], qd = qq[d];
+                    const float kd = to_float(kq[d]), qd = to_float(qq[d]);
                     S[r] = fmaf(keep, S[r], kd * tv);
                     n[r] = fmaf(keep, n[r], take * kd);
                     num = fmaf(S[r], qd, num);
@@ -129,11 +188,17 @@ matrix_memory_scan_kernel(const A* __restrict__ qkv, const float* __restrict__ g
                 nq += __shfl_xor_sync(0xffffffffu, nq, o);
             }
             if (lane == 0 && col_ok) {
-                const float den = fmaxf(fabsf(nq), expf(-m)) + a.floor;
-                out[(size_t)(base + t) * a.heads * a.vdim + (size_t)head * a.vdim + col] = num / den;
+                // q carries the scale dim^-1/2: applied to the two sums instead of to every q
+                const float den = fmaxf(fabsf(nq * a.q_scale), expf(-m)) + a.floor;
+                out[(size_t)(base + t) * a.heads * a.vdim + (size_t)head * a.vdim + col] =
+                    num * a.q_scale / den;
             }
         }
+        if (tid < cnt_next)
+            gate_values(zi, zf, i_s[(buf ^ 1) * MM_CHUNK + tid], f_s[(buf ^ 1) * MM_CHUNK + tid]);
+        __syncthreads();
     }
+    cp_async_wait<0>();
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         const int d = lane + MM_LANES * r;
@@ -157,17 +222,36 @@ MSTAR_API int mstar_matrix_memory_scan(const void* qkv, int act_dtype, int ld, i
     if (state_stride < (long long)heads * ((long long)dim * vdim + dim + 1)) return -1;
     cudaStream_t s = (cudaStream_t)stream;
     MemArgs a{heads, dim, vdim, ld, k_off, v_off, cap, q_scale, floor, state_stride};
-    const size_t smem = sizeof(float) * ((size_t)2 * MM_CHUNK * dim + MM_CHUNK * MM_COLS + 2 * MM_CHUNK);
-    dim3 grid((vdim + MM_COLS - 1) / MM_COLS, heads, entries);
-#define LAUNCH(A, R)                                                                             \
-    mstar_launch((matrix_memory_scan_kernel<A, R>), grid, dim3(MM_THREADS), smem, s, (const A*)qkv, \
-                 gates, bias, qo_indptr, slots, state, out, a)
-#define PICK(A)                                                                                  \
-    if (dim <= 64) { LAUNCH(A, 8); }                                                             \
-    else if (dim <= 128) { LAUNCH(A, 16); }                                                      \
-    else if (dim <= 256) { LAUNCH(A, 32); }                                                      \
-    else { LAUNCH(A, 64); }
-    if (act_dtype == MSTAR_F32) { PICK(float) } else { PICK(bf16) }
+    // Where the batch fills the GPU twice over: 32 columns a block, a column's rows on 8 lanes.
+    // Else (a few long sequences): 8 columns a block and a whole warp per column, so that the
+    // chains spread over four times as many SMs, a step is a quarter of the instructions, and
+    // several warps share a scheduler to hide one another's latencies.
+    const bool wide = (long long)((vdim + 31) / 32) * heads * entries >= 2LL * device_sm_count();
+    const int cols = wide ? 32 : 8;
+    const size_t elem = act_dtype == MSTAR_F32 ? 4 : 2;
+    const size_t smem = 2 * elem * ((size_t)2 * MM_CHUNK * dim + MM_CHUNK * cols) + sizeof(float) * 4 * MM_CHUNK;
+    dim3 grid((vdim + cols - 1) / cols, heads, entries);
+#define LAUNCH(A, R, C, L)                                                                       \
+    {                                                                                            \
+        static size_t configured = 0; /* largest dynamic shared memory set so far */             \
+        if (smem > 48 * 1024 && smem > configured) {                                             \
+            cudaFuncSetAttribute(matrix_memory_scan_kernel<A, R, C, L>,                          \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
+            configured = smem;                                                                   \
+        }                                                                                        \
+        mstar_launch((matrix_memory_scan_kernel<A, R, C, L>), grid, dim3(C * L), smem, s,        \
+                     (const A*)qkv, gates, bias, qo_indptr, slots, state, out, a);               \
+    }
+#define PICK(A, C, L)                                                                            \
+    if (dim <= 64) { LAUNCH(A, 64 / L, C, L); }                                                  \
+    else if (dim <= 128) { LAUNCH(A, 128 / L, C, L); }                                           \
+    else if (dim <= 256) { LAUNCH(A, 256 / L, C, L); }                                           \
+    else { LAUNCH(A, 512 / L, C, L); }
+    if (act_dtype == MSTAR_F32) {
+        if (wide) { PICK(float, 32, 8) } else { PICK(float, 8, 32) }
+    } else {
+        if (wide) { PICK(bf16, 32, 8) } else { PICK(bf16, 8, 32) }
+    }
 #undef PICK
 #undef LAUNCH
     return launch_status();

@@ -85,14 +85,29 @@ expert_gate_up_kernel(const A* __restrict__ x, const A* __restrict__ w_gate_up,
     const int e = chosen[row];
     const float w = scale_input ? weight[row] : 1.f;
     const A* base = w_gate_up + (size_t)e * 2 * ff * width;
+    // rows start at multiples of `width` elements: 8-element loads where that is aligned
+    const bool vec = width % 8 == 0 && ((uintptr_t)w_gate_up & 31) == 0;
     for (int u = blockIdx.y * RE_UNITS + warp; u < min(ff, (int)(blockIdx.y + 1) * RE_UNITS);
          u += RE_THREADS / 32) {
         const A* g = base + (size_t)u * width;
         const A* p = base + (size_t)(ff + u) * width;
         float sg = 0.f, su = 0.f;
-        for (int i = lane; i < width; i += 32) {
-            sg = fmaf(to_float(g[i]), xs[i], sg);
-            su = fmaf(to_float(p[i]), xs[i], su);
+        if (vec) {
+            for (int c = lane; c < (width >> 3); c += 32) {
+                float a8[8], b8[8];
+                load8(g + 8 * c, a8);
+                load8(p + 8 * c, b8);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    sg = fmaf(a8[i], xs[8 * c + i], sg);
+                    su = fmaf(b8[i], xs[8 * c + i], su);
+                }
+            }
+        } else {
+            for (int i = lane; i < width; i += 32) {
+                sg = fmaf(to_float(g[i]), xs[i], sg);
+                su = fmaf(to_float(p[i]), xs[i], su);
+            }
         }
         sg = warp_sum(sg) * w;
         su = warp_sum(su) * w;
@@ -115,6 +130,7 @@ expert_down_kernel(const float* __restrict__ act, const A* __restrict__ w_down,
     add = pdl_after(add, waited);
     for (int i = threadIdx.x; i < top * ff; i += RE_THREADS) as[i] = act[(size_t)t * top * ff + i];
     __syncthreads();
+    const bool vec = ff % 8 == 0 && ((uintptr_t)w_down & 31) == 0;
     for (int c = blockIdx.y * RE_UNITS + warp; c < min(width, (int)(blockIdx.y + 1) * RE_UNITS);
          c += RE_THREADS / 32) {
         float total = 0.f;
@@ -122,7 +138,16 @@ expert_down_kernel(const float* __restrict__ act, const A* __restrict__ w_down,
             const int e = chosen[(size_t)t * top + k];
             const A* wrow = w_down + ((size_t)e * width + c) * ff;
             float s = 0.f;
-            for (int j = lane; j < ff; j += 32) s = fmaf(to_float(wrow[j]), as[k * ff + j], s);
+            if (vec) {
+                for (int c2 = lane; c2 < (ff >> 3); c2 += 32) {
+                    float a8[8];
+                    load8(wrow + 8 * c2, a8);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) s = fmaf(a8[i], as[k * ff + 8 * c2 + i], s);
+                }
+            } else {
+                for (int j = lane; j < ff; j += 32) s = fmaf(to_float(wrow[j]), as[k * ff + j], s);
+            }
             s = warp_sum(s);
             total += scale_input ? s : s * weight[(size_t)t * top + k];
         }

@@ -814,29 +814,60 @@ def latent_fill(proj: torch.Tensor, dkv_offset: int, norm_weight: torch.Tensor, 
     check(code, "latent_fill")
 
 
+def latent_attention_plan(tokens: int, heads: int, rank: int, max_keys: int,
+                          sms: int | None = None) -> tuple:
+    """(heads per block, splits of a token's keys) for the latent attention kernel: with many
+    tokens a block takes as many heads as its registers hold (they share the rows it loads)
+    and all keys; with few, smaller groups and shared keys until there are some two blocks
+    per SM, a split keeping at least two tiles of 32 keys."""
+    if sms is None:
+        sms = num_sms()
+    group = max(1, min(heads, 16 if rank <= 256 else (8 if rank <= 512 else 4)))
+    want = 2 * sms
+    while group > 4 and tokens * -(-heads // group) < want:
+        group = max(4, group // 2)
+    blocks = tokens * -(-heads // group)
+    tiles = max(1, -(-max_keys // 32))
+    splits = max(1, min(want // max(blocks, 1), tiles // 2, 32))
+    return group, splits
+
+
 def latent_attention(q_abs: torch.Tensor, q_rot: torch.Tensor, cache: torch.Tensor, block_table,
                      token_req, cache_pos, heads: int, rank: int, rot: int, page_size: int,
-                     window: int, scale: float) -> torch.Tensor:
+                     window: int, scale: float, max_keys: int | None = None) -> torch.Tensor:
     """Softmax attention of every token over the latent rows it sees.  ``q_abs``: float
     [tokens, heads, rank], the plain query part with the key up-projection folded in;
     ``q_rot``: [tokens, heads, rot] view (last stride 1) of rotated query parts.  Returns the
-    float [tokens, heads, rank] probability-weighted sums of latents."""
+    float [tokens, heads, rank] probability-weighted sums of latents.  ``max_keys`` bounds the
+    keys any token sees (default: the window, or one tile when there is none); it only decides
+    among how many blocks a token's keys are shared."""
     _need_cuda(q_abs, q_rot, cache, block_table, token_req, cache_pos)
     assert q_abs.dtype == torch.float32 and q_abs.is_contiguous()
     tokens = q_abs.shape[0]
     assert tuple(q_abs.shape) == (tokens, heads, rank) and cache.is_contiguous()
     assert tuple(q_rot.shape) == (tokens, heads, rot) and q_rot.dtype == cache.dtype
     assert rot == 0 or q_rot.stride(2) == 1
+    if max_keys is None:
+        max_keys = window or 32
+    if window:
+        max_keys = min(max_keys, window)
+    group, splits = latent_attention_plan(tokens, heads, rank, max_keys, num_sms(q_abs.device))
     out = torch.empty((tokens, heads, rank), dtype=torch.float32, device=q_abs.device)
+    scratch = None
+    if splits > 1:
+        scratch = torch.empty(tokens * heads * splits * (rank + 2), dtype=torch.float32,
+                              device=q_abs.device)
     code = lib.get("attention_latent").mstar_latent_attention(
         q_abs.data_ptr(), q_rot.data_ptr(), q_rot.stride(0), q_rot.stride(1), out.data_ptr(),
         cache.data_ptr(), block_table.data_ptr(), block_table.stride(0), token_req.data_ptr(),
         cache_pos.data_ptr(), tokens, heads, rank, rot, page_size, int(window or 0), float(scale),
-        _dt(cache), _stream())
+        _dt(cache), group, splits, _ptr(scratch), _stream())
     if code == -1:
-        raise KernelError(f"latent attention refuses rank={rank}, rot={rot} (rank at most 4096, "
+        raise KernelError(f"latent attention refuses rank={rank}, rot={rot} (rank at most 1024, "
                           "a tile of 32 rows within 200 KB of shared memory)")
     check(code, "latent_attention")
+    if splits > 1:
+        lib.add_launches(1)                     # the merge kernel
     return out
 
 

@@ -75,7 +75,8 @@ class LatentAttention:
         q_abs = ops.linear_per_head(q[:, :, :s.qk_dim], self.uk_t, out_dtype=torch.float32)
         lat = ops.latent_attention(q_abs, q[:, :, s.qk_dim:], cache.kv, cache.block_table,
                                    ctx.token_req, ctx.cache_pos, h, s.kv_rank, s.rot_dim,
-                                   cache.page_size, s.window or 0, self.scale)
+                                   cache.page_size, s.window or 0, self.scale,
+                                   max_keys=ctx.max_kv_len)
         y = ops.linear_per_head(ops.convert(lat, self.runtime.dtype), self.uv)
         y = y.view(-1, h * s.v_dim)
         if s.gated:
