@@ -20,6 +20,7 @@
 // (RMS, plain weight), rotates the shared key part and the rotated part of every query head
 // (pairs (2i, 2i+1), angle = position * freq_i in double precision), and writes the row.
 #include "common.cuh"
+#include "mma_util.cuh"
 
 #define LAT_TILE 32
 #define LAT_THREADS 128
@@ -218,6 +219,164 @@ latent_attention_kernel(const float* __restrict__ q_abs, const A* __restrict__ q
     }
 }
 
+// The same attention for a bfloat16 cache whose rows are whole k-steps (D a multiple of 16):
+// the rows stay bfloat16 in shared memory (asynchronous 16-byte copies), and the scores are
+// made on the tensor cores (mma.sync m16n8k16, float sums).  The query's folded part is float:
+// it is split into a bfloat16 head and a bfloat16 remainder, each multiplied with the keys, so
+// that nothing of it is rounded away.  The softmax and the weighted sum of the latents are as in
+// the kernel above: float, a thread keeping GP x CPT sums.
+template <int GP>
+__global__ void __launch_bounds__(LAT_THREADS)
+latent_attention_mma_kernel(const float* __restrict__ q_abs, const bf16* __restrict__ q_rot,
+                            float* __restrict__ out, float* __restrict__ part_acc,
+                            float* __restrict__ part_ml, const bf16* __restrict__ cache,
+                            const int* __restrict__ block_table, const int* __restrict__ token_req,
+                            const int* __restrict__ cache_pos, LatentArgs a) {
+    constexpr int CPT = LAT_MAX_ACC / GP;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int t = blockIdx.x, h0 = blockIdx.y * a.group, split = blockIdx.z;
+    const int G = min(a.group, a.heads - h0);
+    const int D = a.rank + a.rot, DP = D + 8;          // 16 bytes of padding: no bank conflicts
+    bf16* qh = reinterpret_cast<bf16*>(smem_raw);      // [16][DP] head of the query
+    bf16* ql = qh + 16 * DP;                           // [16][DP] remainder
+    bf16* tile = ql + 16 * DP;                         // [TILE][DP]
+    float* sc = reinterpret_cast<float*>(tile + LAT_TILE * DP);   // [TILE][GP]
+    float* m_s = sc + LAT_TILE * GP;
+    float* l_s = m_s + GP;
+    float* alpha_s = l_s + GP;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const unsigned long long waited = pdl_wait();
+    q_abs = pdl_after(q_abs, waited);
+    q_rot = pdl_after(q_rot, waited);
+    cache = pdl_after(cache, waited);
+
+    const int hi = cache_pos[t] + 1;
+    const int lo = (a.window > 0 && hi > a.window) ? hi - a.window : 0;
+    const int* bt = block_table + (size_t)token_req[t] * a.bt_stride;
+
+    for (int i = tid; i < 16 * D; i += LAT_THREADS) {
+        const int g = i / D, d = i - g * D;
+        float v = 0.f;
+        if (g < G)
+            v = d < a.rank ? q_abs[((size_t)t * a.heads + h0 + g) * a.rank + d]
+                           : to_float(q_rot[(size_t)t * a.ldq + (size_t)(h0 + g) * a.q_head + (d - a.rank)]);
+        const bf16 head = __float2bfloat16_rn(v);
+        qh[g * DP + d] = head;
+        ql[g * DP + d] = __float2bfloat16_rn(v - __bfloat162float(head));
+    }
+    for (int i = tid; i < GP; i += LAT_THREADS) {
+        m_s[i] = -INFINITY;
+        l_s[i] = 0.f;
+    }
+    float acc[CPT][GP];
+#pragma unroll
+    for (int c = 0; c < CPT; ++c)
+#pragma unroll
+        for (int g = 0; g < GP; ++g) acc[c][g] = 0.f;
+    const int chunks = D >> 3;
+
+    for (int base = lo + split * LAT_TILE; base < hi; base += a.splits * LAT_TILE) {
+        __syncthreads();                               // the tile of the round before is done with
+        for (int idx = tid; idx < LAT_TILE * chunks; idx += LAT_THREADS) {
+            const int j = idx / chunks, c = idx - j * chunks;
+            const int key = base + j;
+            const bf16* src = cache;
+            if (key < hi)
+                src = cache + ((size_t)bt[key / a.page_size] * a.page_size + key % a.page_size) * D + c * 8;
+            cp_async_16(smem_u32(tile + j * DP + c * 8), src, key < hi ? 16 : 0);
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+        __syncthreads();
+        // scores: warp w takes keys 8w .. 8w+7 and all 16 head rows
+        {
+            float s4[4] = {0.f, 0.f, 0.f, 0.f};
+            const int arow = lane & 15, acol = (lane >> 4) * 8;
+            const int brow = warp * 8 + (lane & 7), bcol = ((lane >> 3) & 1) * 8;
+            for (int k0 = 0; k0 < D; k0 += 16) {
+                uint32_t ah[4], al[4], b0, b1;
+                ldmatrix_x4(ah, smem_u32(qh + arow * DP + k0 + acol));
+                ldmatrix_x4(al, smem_u32(ql + arow * DP + k0 + acol));
+                asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n"
+                             : "=r"(b0), "=r"(b1)
+                             : "r"(smem_u32(tile + brow * DP + k0 + bcol)));
+                mma_bf16_16816(s4, ah, b0, b1);
+                mma_bf16_16816(s4, al, b0, b1);
+            }
+            const int g = lane >> 2, j0 = warp * 8 + 2 * (lane & 3);
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int head = g + 8 * half;
+                if (head < GP) {
+                    sc[j0 * GP + head] = base + j0 < hi ? s4[2 * half] * a.scale : -INFINITY;
+                    sc[(j0 + 1) * GP + head] = base + j0 + 1 < hi ? s4[2 * half + 1] * a.scale : -INFINITY;
+                }
+            }
+        }
+        __syncthreads();
+        for (int g = warp; g < GP; g += LAT_THREADS / 32) {
+            const float s = sc[lane * GP + g];
+            const float m_old = m_s[g];
+            const float m_new = fmaxf(m_old, warp_max(s));   // key `base` is always valid
+            const float p = expf(s - m_new);
+            const float psum = warp_sum(p);
+            sc[lane * GP + g] = p;
+            if (lane == 0) {
+                const float al = expf(m_old - m_new);
+                alpha_s[g] = al;
+                l_s[g] = l_s[g] * al + psum;
+                m_s[g] = m_new;
+            }
+        }
+        __syncthreads();
+        {
+            float al[GP];
+#pragma unroll
+            for (int g = 0; g < GP; ++g) al[g] = alpha_s[g];
+#pragma unroll
+            for (int c = 0; c < CPT; ++c)
+#pragma unroll
+                for (int g = 0; g < GP; ++g) acc[c][g] *= al[g];
+        }
+#pragma unroll 2
+        for (int j = 0; j < LAT_TILE; ++j) {
+            float p[GP];
+#pragma unroll
+            for (int q4 = 0; q4 < GP / 4; ++q4) {
+                const float4 v = *reinterpret_cast<const float4*>(sc + j * GP + 4 * q4);
+                p[4 * q4] = v.x; p[4 * q4 + 1] = v.y; p[4 * q4 + 2] = v.z; p[4 * q4 + 3] = v.w;
+            }
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) {
+                const int d = tid + c * LAT_THREADS;
+                const float v = d < a.rank ? __bfloat162float(tile[j * DP + d]) : 0.f;
+#pragma unroll
+                for (int g = 0; g < GP; ++g) acc[c][g] = fmaf(p[g], v, acc[c][g]);
+            }
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) {
+        const int d = tid + c * LAT_THREADS;
+        if (d >= a.rank) continue;
+#pragma unroll
+        for (int g = 0; g < GP; ++g) {
+            if (g >= G) continue;
+            const size_t th = (size_t)t * a.heads + h0 + g;
+            if (a.splits == 1) {
+                out[th * a.rank + d] = acc[c][g] / l_s[g];
+            } else {
+                part_acc[(th * a.splits + split) * a.rank + d] = acc[c][g];
+                if (d == 0) {
+                    part_ml[(th * a.splits + split) * 2] = m_s[g];
+                    part_ml[(th * a.splits + split) * 2 + 1] = l_s[g];
+                }
+            }
+        }
+    }
+}
+
 // out[t, h, :] = sum_s exp(m_s - M) acc_s / sum_s exp(m_s - M) l_s, in the order of the splits.
 // A split that saw no key has l = 0 and m = -inf and adds nothing.
 __global__ void latent_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
@@ -288,6 +447,36 @@ MSTAR_API int mstar_latent_attention(const float* q_abs, const void* q_rot, int 
     dim3 grid(num_tokens, (heads + group - 1) / group, splits);
     float* part_acc = scratch;
     float* part_ml = scratch == nullptr ? nullptr : scratch + (size_t)num_tokens * heads * splits * rank;
+    // a bfloat16 cache with rows of whole k-steps: scores on the tensor cores
+    // (MSTAR_LATENT_ATTENTION=cores keeps the kernel above)
+    static int cores_only = -1;
+    if (cores_only < 0) {
+        const char* e = getenv("MSTAR_LATENT_ATTENTION");
+        cores_only = (e != nullptr && e[0] == 'c') ? 1 : 0;
+    }
+    const size_t smem_mma = sizeof(bf16) * (size_t)(32 + LAT_TILE) * (D + 8) +
+                            sizeof(float) * ((size_t)gp * LAT_TILE + 3 * (size_t)gp);
+    if (act_dtype == MSTAR_BF16 && D % 16 == 0 && ((uintptr_t)cache & 15) == 0 && !cores_only &&
+        smem_mma <= 200 * 1024) {
+#define GO_MMA(GP)                                                                                \
+    {                                                                                             \
+        static size_t configured = 0;                                                             \
+        if (smem_mma > 48 * 1024 && smem_mma > configured) {                                      \
+            cudaFuncSetAttribute(latent_attention_mma_kernel<GP>,                                 \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_mma);     \
+            configured = smem_mma;                                                                \
+        }                                                                                         \
+        mstar_launch((latent_attention_mma_kernel<GP>), grid, dim3(LAT_THREADS), smem_mma, s,     \
+                     q_abs, (const bf16*)q_rot, out, part_acc, part_ml, (const bf16*)cache,       \
+                     block_table, token_req, cache_pos, a);                                       \
+    }
+        if (gp == 4) GO_MMA(4) else if (gp == 8) GO_MMA(8) else GO_MMA(16)
+#undef GO_MMA
+        if (splits > 1)
+            mstar_launch(latent_merge_kernel, dim3(num_tokens * heads), dim3(128), 0, s,
+                         (const float*)part_acc, (const float*)part_ml, out, rank, splits);
+        return launch_status();
+    }
 #define GO(A, GP) launch_latent<A, GP>(q_abs, q_rot, out, part_acc, part_ml, cache, block_table, \
                                        token_req, cache_pos, a, grid, smem, s)
     if (act_dtype == MSTAR_F32) {
