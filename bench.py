@@ -672,6 +672,46 @@ def kernel_bench(name: str, batch: int, ctx: int, small: bool, cfg: dict) -> int
             fn = lambda: ops.rope_kv_write(qkv, pos, pos, req, table, inv, kv, nq, nkv, hd, hd,
                                            False, PAGE_SIZE)
         out.update(ms=_time_graph(fn, reps=50))
+    elif name in ("matrix_memory_scan", "latent_attention"):
+        # kernels of the Tifosun decoder at its medium layer sizes: --batch sequences of --ctx
+        # new tokens each (the scan), or --batch requests whose last --ctx tokens attend over a
+        # cache of max(--ctx, 2,048) rows (the attention); --ctx 1 is a decode step
+        t_cfg, _ = tifosun_sizes("small" if small else "medium")
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        per = ctx
+        if name == "matrix_memory_scan":
+            m = next(l["mixer"] for l in t_cfg["layers"] if l["type"] == "mlstm")
+            Hm, dim, vdim = m["heads"], m["dim"], m["vdim"]
+            size = ops.matrix_memory_state_size(Hm, dim, vdim)
+            state = torch.zeros(batch + 1, size, device=dev)
+            proj = rnd(batch * per, 2 * Hm * dim + 2 * Hm * vdim)
+            gates = torch.randn(batch * per, 2 * Hm, device=dev)
+            bias = torch.zeros(2 * Hm, device=dev)
+            indptr, slots = i32([k * per for k in range(batch + 1)]), i32(list(range(batch)))
+            fn = lambda: ops.matrix_memory_scan(proj, gates, bias, indptr, slots, state, batch, Hm,
+                                                dim, vdim, 15.0, dim ** -0.5, 1e-6)
+            ms = _time_graph(fn, reps=4)
+            out.update(ms=ms, heads=Hm, dim=dim, vdim=vdim, tokens_per_us_per_chain=per / ms / 1e3,
+                       state_gbs=2.0 * batch * size * 4 / ms / 1e6)
+        else:
+            m = next(l["mixer"] for l in t_cfg["layers"] if l["type"] == "latent_attention")
+            heads, rank, rot, window = m["heads"], m["kv_rank"], m["rot_dim"], m["mask"]["size"]
+            length = max(ctx, PROMPT_LEN)
+            pages_per = -(-length // PAGE_SIZE)
+            cache = rnd(batch * pages_per + 1, 1, 1, PAGE_SIZE, rank + rot)
+            table = torch.randperm(batch * pages_per, device=dev).to(torch.int32).view(batch, -1)
+            token_req = i32([r for r in range(batch) for _ in range(per)])
+            cache_pos = i32([length - per + k for _ in range(batch) for k in range(per)])
+            q_abs = torch.randn(batch * per, heads, rank, device=dev)
+            q_rot = rnd(batch * per, heads, rot)
+            fn = lambda: ops.latent_attention(q_abs, q_rot, cache, table, token_req, cache_pos, heads,
+                                              rank, rot, PAGE_SIZE, window, m["scale"],
+                                              max_keys=length)
+            ms = _time_graph(fn, reps=4)
+            keys = sum(min(length - per + k + 1, window) for k in range(per)) * batch
+            flops = 2.0 * heads * keys * (2 * rank + rot)
+            out.update(ms=ms, heads=heads, rank=rank, rot=rot, window=window,
+                       tflops=flops / ms / 1e9, frac_bf16=flops / ms / 1e9 / pk["bf16_tflops"])
     else:
         print(f"unknown kernel {name!r}")
         return 2
@@ -720,7 +760,8 @@ def main() -> int:
     ap.add_argument("--kernel", default=None,
                     help="time one kernel alone (decode_attention, prefill_attention, gemm_qkv, "
                          "gemm_o, gemm_gate_up, gemm_down, gemm_lm_head, qkv_rope, add_rmsnorm, "
-                         "rope_kv_write) at --batch rows / requests and --ctx keys")
+                         "rope_kv_write, matrix_memory_scan, latent_attention) at --batch rows / "
+                         "requests and --ctx keys")
     ap.add_argument("--ctx", type=int, default=PROMPT_LEN)
     ap.add_argument("--small", action="store_true", help="a smaller case, for profiler captures")
     ap.add_argument("--sizes", default="orpheus-3b", choices=sorted(SIZES),

@@ -49,28 +49,28 @@ __device__ __forceinline__ void stage_vec(A* dst, const A* src, int n, int first
     for (int c = first; c < n / V; c += step) cp_async_16(smem_u32(dst + c * V), src + c * V, 16);
 }
 
-template <typename A, int R, int MM_COLS, int MM_LANES>
+// MM_COLS x CT value columns a block (CT columns a thread), a column's rows on MM_LANES lanes.
+template <typename A, int R, int MM_COLS, int MM_LANES, int CT>
 __global__ void __launch_bounds__(MM_COLS * MM_LANES)
 matrix_memory_scan_kernel(const A* __restrict__ qkv, const float* __restrict__ gates,
                           const float* __restrict__ bias, const int* __restrict__ qo_indptr,
                           const int* __restrict__ slots, float* __restrict__ state,
                           float* __restrict__ out, MemArgs a) {
     constexpr int MM_THREADS = MM_COLS * MM_LANES;
+    constexpr int BCOLS = MM_COLS * CT;                   // columns of the block
     constexpr int V = 16 / (int)sizeof(A);
     // two stages of a chunk's q, k (this head) and v (this block's columns) as they are in
     // memory, and of its gates: the next chunk is copied while this one is walked
     extern __shared__ __align__(16) unsigned char smem_raw[];
     A* q_s = reinterpret_cast<A*>(smem_raw);              // [2][CHUNK][dim]
     A* k_s = q_s + 2 * MM_CHUNK * a.dim;                  // [2][CHUNK][dim]
-    A* v_s = k_s + 2 * MM_CHUNK * a.dim;                  // [2][CHUNK][COLS]
-    float* i_s = reinterpret_cast<float*>(v_s + 2 * MM_CHUNK * MM_COLS);   // [2][CHUNK]
+    A* v_s = k_s + 2 * MM_CHUNK * a.dim;                  // [2][CHUNK][BCOLS]
+    float* i_s = reinterpret_cast<float*>(v_s + 2 * MM_CHUNK * BCOLS);   // [2][CHUNK]
     float* f_s = i_s + 2 * MM_CHUNK;                      // [2][CHUNK]
 
     const int entry = blockIdx.z, head = blockIdx.y;
     const int tid = threadIdx.x, lane = tid % MM_LANES, colb = tid / MM_LANES;
-    const int col0 = blockIdx.x * MM_COLS;
-    const int col = col0 + colb;
-    const bool col_ok = col < a.vdim;
+    const int col0 = blockIdx.x * BCOLS;
     const int t0 = qo_indptr[entry], t1 = qo_indptr[entry + 1];
     // the state is an earlier step's, but the slot may have been zeroed just now: everything
     // but the step's index arrays is read after the wait
@@ -79,19 +79,27 @@ matrix_memory_scan_kernel(const A* __restrict__ qkv, const float* __restrict__ g
     gates = pdl_after(gates, waited);
     state = pdl_after(state, waited);
     float* slot = state + (size_t)slots[entry] * a.state_stride;
-    float* S_g = slot + ((size_t)head * a.vdim + (col_ok ? col : 0)) * a.dim;
     float* n_g = slot + (size_t)a.heads * a.vdim * a.dim + (size_t)head * a.dim;
     float* m_g = n_g + (size_t)a.heads * a.dim - (size_t)head * a.dim + head;
+    float* S_g[CT];
+    bool col_ok[CT];
+#pragma unroll
+    for (int c = 0; c < CT; ++c) {
+        const int col = col0 + colb * CT + c;
+        col_ok[c] = col < a.vdim;
+        S_g[c] = slot + ((size_t)head * a.vdim + (col_ok[c] ? col : 0)) * a.dim;
+    }
 
     // 16-byte copies where rows and columns start on 16-byte boundaries, else element by element
     const bool base_ok = ((uintptr_t)qkv & 15) == 0 && a.ld % V == 0;
     const bool qk_vec = base_ok && a.dim % V == 0 && a.k_off % V == 0;
-    const bool v_vec = base_ok && (a.v_off + head * a.vdim + col0) % V == 0 && col0 + MM_COLS <= a.vdim;
+    const bool v_vec = base_ok && (a.v_off + head * a.vdim + col0) % V == 0 && col0 + BCOLS <= a.vdim &&
+                       BCOLS % V == 0;
 
     auto stage = [&](int buf, int base, int cnt) {
         A* qd = q_s + buf * MM_CHUNK * a.dim;
         A* kd = k_s + buf * MM_CHUNK * a.dim;
-        A* vd = v_s + buf * MM_CHUNK * MM_COLS;
+        A* vd = v_s + buf * MM_CHUNK * BCOLS;
         if (qk_vec) {
             const int per = a.dim / V;
             for (int idx = tid; idx < cnt * per; idx += MM_THREADS) {
@@ -109,15 +117,15 @@ matrix_memory_scan_kernel(const A* __restrict__ qkv, const float* __restrict__ g
             }
         }
         if (v_vec) {
-            constexpr int per = MM_COLS / V;
+            constexpr int per = BCOLS / V > 0 ? BCOLS / V : 1;
             for (int idx = tid; idx < cnt * per; idx += MM_THREADS) {
                 const int t = idx / per, c = idx - t * per;
-                cp_async_16(smem_u32(vd + t * MM_COLS + c * V),
+                cp_async_16(smem_u32(vd + t * BCOLS + c * V),
                             qkv + (size_t)(base + t) * a.ld + a.v_off + (size_t)head * a.vdim + col0 + c * V, 16);
             }
         } else {
-            for (int idx = tid; idx < cnt * MM_COLS; idx += MM_THREADS) {
-                const int t = idx / MM_COLS, c = idx - t * MM_COLS;
+            for (int idx = tid; idx < cnt * BCOLS; idx += MM_THREADS) {
+                const int t = idx / BCOLS, c = idx - t * BCOLS;
                 vd[idx] = col0 + c < a.vdim ? qkv[(size_t)(base + t) * a.ld + a.v_off +
                                                   (size_t)head * a.vdim + col0 + c]
                                             : from_float<A>(0.f);
@@ -129,11 +137,12 @@ matrix_memory_scan_kernel(const A* __restrict__ qkv, const float* __restrict__ g
         fg = log_sigmoid(soft_cap(zf + bias[a.heads + head], a.cap));
     };
 
-    float S[R], n[R];
+    float S[CT][R], n[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         const int d = lane + MM_LANES * r;
-        S[r] = (col_ok && d < a.dim) ? S_g[d] : 0.f;
+#pragma unroll
+        for (int c = 0; c < CT; ++c) S[c][r] = (col_ok[c] && d < a.dim) ? S_g[c][d] : 0.f;
         n[r] = d < a.dim ? n_g[d] : 0.f;
     }
     float m = *m_g;
@@ -145,8 +154,8 @@ matrix_memory_scan_kernel(const A* __restrict__ qkv, const float* __restrict__ g
         const float* g = gates + (size_t)(t0 + tid) * 2 * a.heads;
         gate_values(g[head], g[a.heads + head], i_s[tid], f_s[tid]);
     }
-    for (int c = 0; c < chunks; ++c) {
-        const int buf = c & 1, base = t0 + c * MM_CHUNK;
+    for (int ch = 0; ch < chunks; ++ch) {
+        const int buf = ch & 1, base = t0 + ch * MM_CHUNK;
         const int cnt = min(MM_CHUNK, t1 - base);
         const int cnt_next = min(MM_CHUNK, t1 - base - MM_CHUNK);     // <= 0 after the last chunk
         if (cnt_next > 0) stage(buf ^ 1, base + MM_CHUNK, cnt_next);
@@ -161,37 +170,49 @@ matrix_memory_scan_kernel(const A* __restrict__ qkv, const float* __restrict__ g
         __syncthreads();
         const A* kb = k_s + buf * MM_CHUNK * a.dim;
         const A* qb = q_s + buf * MM_CHUNK * a.dim;
-        const A* vb = v_s + buf * MM_CHUNK * MM_COLS;
+        const A* vb = v_s + buf * MM_CHUNK * BCOLS;
         for (int t = 0; t < cnt; ++t) {
             const float fg = f_s[buf * MM_CHUNK + t], ig = i_s[buf * MM_CHUNK + t];
             const float m_new = fmaxf(fg + m, ig);
             const float keep = expf(fg + m - m_new), take = expf(ig - m_new);
             m = m_new;
-            const float tv = take * to_float(vb[t * MM_COLS + colb]);
+            float v[CT], num[CT];
+#pragma unroll
+            for (int c = 0; c < CT; ++c) {
+                v[c] = to_float(vb[t * BCOLS + colb * CT + c]);
+                num[c] = 0.f;
+            }
             const A* kq = kb + t * a.dim;
             const A* qq = qb + t * a.dim;
-            float num = 0.f, nq = 0.f;
+            float nq = 0.f;
 #pragma unroll
             for (int r = 0; r < R; ++r) {
                 const int d = lane + MM_LANES * r;
                 if (d < a.dim) {
-                    const float kd = to_float(kq[d]), qd = to_float(qq[d]);
-                    S[r] = fmaf(keep, S[r], kd * tv);
-                    n[r] = fmaf(keep, n[r], take * kd);
-                    num = fmaf(S[r], qd, num);
+                    const float tk = take * to_float(kq[d]), qd = to_float(qq[d]);
+                    n[r] = fmaf(keep, n[r], tk);
                     nq = fmaf(n[r], qd, nq);
+#pragma unroll
+                    for (int c = 0; c < CT; ++c) {
+                        S[c][r] = fmaf(keep, S[c][r], tk * v[c]);
+                        num[c] = fmaf(S[c][r], qd, num[c]);
+                    }
                 }
             }
 #pragma unroll
             for (int o = 1; o < MM_LANES; o <<= 1) {
-                num += __shfl_xor_sync(0xffffffffu, num, o);
                 nq += __shfl_xor_sync(0xffffffffu, nq, o);
+#pragma unroll
+                for (int c = 0; c < CT; ++c) num[c] += __shfl_xor_sync(0xffffffffu, num[c], o);
             }
-            if (lane == 0 && col_ok) {
-                // q carries the scale dim^-1/2: applied to the two sums instead of to every q
+            if (lane == 0) {
+                // q carries the scale dim^-1/2: applied to the sums instead of to every q
                 const float den = fmaxf(fabsf(nq * a.q_scale), expf(-m)) + a.floor;
-                out[(size_t)(base + t) * a.heads * a.vdim + (size_t)head * a.vdim + col] =
-                    num * a.q_scale / den;
+                float* orow = out + (size_t)(base + t) * a.heads * a.vdim + (size_t)head * a.vdim +
+                              col0 + colb * CT;
+#pragma unroll
+                for (int c = 0; c < CT; ++c)
+                    if (col_ok[c]) orow[c] = num[c] * a.q_scale / den;
             }
         }
         if (tid < cnt_next)
@@ -203,7 +224,9 @@ matrix_memory_scan_kernel(const A* __restrict__ qkv, const float* __restrict__ g
     for (int r = 0; r < R; ++r) {
         const int d = lane + MM_LANES * r;
         if (d < a.dim) {
-            if (col_ok) S_g[d] = S[r];
+#pragma unroll
+            for (int c = 0; c < CT; ++c)
+                if (col_ok[c]) S_g[c][d] = S[c][r];
             if (blockIdx.x == 0 && colb == 0) n_g[d] = n[r];
         }
     }
@@ -225,32 +248,36 @@ MSTAR_API int mstar_matrix_memory_scan(const void* qkv, int act_dtype, int ld, i
     // Where the batch fills the GPU twice over: 32 columns a block, a column's rows on 8 lanes.
     // Else (a few long sequences): 8 columns a block and a whole warp per column, so that the
     // chains spread over four times as many SMs, a step is a quarter of the instructions, and
-    // several warps share a scheduler to hide one another's latencies.
+    // the eight warps of a block hide one another's latencies.  (Four columns a thread, which
+    // share the loads of q and k and the sums of n, were tried there: a third of the
+    // instructions per column, but a quarter of the blocks, and 1.70 instead of 1.49 ms for a
+    // prompt of 2,048 tokens at 4 heads of 256 x 512: what counts is the latency of a token's
+    // chain and how many warps there are to hide it.)
     const bool wide = (long long)((vdim + 31) / 32) * heads * entries >= 2LL * device_sm_count();
     const int cols = wide ? 32 : 8;
     const size_t elem = act_dtype == MSTAR_F32 ? 4 : 2;
     const size_t smem = 2 * elem * ((size_t)2 * MM_CHUNK * dim + MM_CHUNK * cols) + sizeof(float) * 4 * MM_CHUNK;
     dim3 grid((vdim + cols - 1) / cols, heads, entries);
-#define LAUNCH(A, R, C, L)                                                                       \
+#define LAUNCH(A, R, C, L, CT)                                                                   \
     {                                                                                            \
         static size_t configured = 0; /* largest dynamic shared memory set so far */             \
         if (smem > 48 * 1024 && smem > configured) {                                             \
-            cudaFuncSetAttribute(matrix_memory_scan_kernel<A, R, C, L>,                          \
+            cudaFuncSetAttribute(matrix_memory_scan_kernel<A, R, C, L, CT>,                      \
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
             configured = smem;                                                                   \
         }                                                                                        \
-        mstar_launch((matrix_memory_scan_kernel<A, R, C, L>), grid, dim3(C * L), smem, s,        \
+        mstar_launch((matrix_memory_scan_kernel<A, R, C, L, CT>), grid, dim3(C * L), smem, s,    \
                      (const A*)qkv, gates, bias, qo_indptr, slots, state, out, a);               \
     }
-#define PICK(A, C, L)                                                                            \
-    if (dim <= 64) { LAUNCH(A, 64 / L, C, L); }                                                  \
-    else if (dim <= 128) { LAUNCH(A, 128 / L, C, L); }                                           \
-    else if (dim <= 256) { LAUNCH(A, 256 / L, C, L); }                                           \
-    else { LAUNCH(A, 512 / L, C, L); }
+#define PICK(A, C, L, CT)                                                                        \
+    if (dim <= 64) { LAUNCH(A, 64 / L, C, L, CT); }                                              \
+    else if (dim <= 128) { LAUNCH(A, 128 / L, C, L, CT); }                                       \
+    else if (dim <= 256) { LAUNCH(A, 256 / L, C, L, CT); }                                       \
+    else { LAUNCH(A, 512 / L, C, L, CT); }
     if (act_dtype == MSTAR_F32) {
-        if (wide) { PICK(float, 32, 8) } else { PICK(float, 8, 32) }
+        if (wide) { PICK(float, 32, 8, 1) } else { PICK(float, 8, 32, 1) }
     } else {
-        if (wide) { PICK(bf16, 32, 8) } else { PICK(bf16, 8, 32) }
+        if (wide) { PICK(bf16, 32, 8, 1) } else { PICK(bf16, 8, 32, 1) }
     }
 #undef PICK
 #undef LAUNCH
