@@ -87,31 +87,44 @@ expert_gate_up_kernel(const A* __restrict__ x, const A* __restrict__ w_gate_up,
     const A* base = w_gate_up + (size_t)e * 2 * ff * width;
     // rows start at multiples of `width` elements: 8-element loads where that is aligned
     const bool vec = width % 8 == 0 && ((uintptr_t)w_gate_up & 31) == 0;
-    for (int u = blockIdx.y * RE_UNITS + warp; u < min(ff, (int)(blockIdx.y + 1) * RE_UNITS);
-         u += RE_THREADS / 32) {
-        const A* g = base + (size_t)u * width;
-        const A* p = base + (size_t)(ff + u) * width;
-        float sg = 0.f, su = 0.f;
+    // a warp takes four hidden units at a time: eight rows of weights stream side by side
+    const int u_end = min(ff, (int)(blockIdx.y + 1) * RE_UNITS);
+    for (int u0 = blockIdx.y * RE_UNITS + warp * 4; u0 < u_end; u0 += (RE_THREADS / 32) * 4) {
+        float sg[4] = {0.f, 0.f, 0.f, 0.f}, su[4] = {0.f, 0.f, 0.f, 0.f};
         if (vec) {
             for (int c = lane; c < (width >> 3); c += 32) {
-                float a8[8], b8[8];
-                load8(g + 8 * c, a8);
-                load8(p + 8 * c, b8);
+                float a8[4][8], b8[4][8];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int u = min(u0 + k, ff - 1);          // a unit past the end repeats the last
+                    load8(base + (size_t)u * width + 8 * c, a8[k]);
+                    load8(base + (size_t)(ff + u) * width + 8 * c, b8[k]);
+                }
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    sg = fmaf(a8[i], xs[8 * c + i], sg);
-                    su = fmaf(b8[i], xs[8 * c + i], su);
+                    const float xv = xs[8 * c + i];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        sg[k] = fmaf(a8[k][i], xv, sg[k]);
+                        su[k] = fmaf(b8[k][i], xv, su[k]);
+                    }
                 }
             }
         } else {
             for (int i = lane; i < width; i += 32) {
-                sg = fmaf(to_float(g[i]), xs[i], sg);
-                su = fmaf(to_float(p[i]), xs[i], su);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int u = min(u0 + k, ff - 1);
+                    sg[k] = fmaf(to_float(base[(size_t)u * width + i]), xs[i], sg[k]);
+                    su[k] = fmaf(to_float(base[(size_t)(ff + u) * width + i]), xs[i], su[k]);
+                }
             }
         }
-        sg = warp_sum(sg) * w;
-        su = warp_sum(su) * w;
-        if (lane == 0) act[(size_t)row * ff + u] = sg / (1.f + expf(-sg)) * su;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float g = warp_sum(sg[k]) * w, up = warp_sum(su[k]) * w;
+            if (lane == 0 && u0 + k < u_end) act[(size_t)row * ff + u0 + k] = g / (1.f + expf(-g)) * up;
+        }
     }
 }
 
@@ -131,29 +144,47 @@ expert_down_kernel(const float* __restrict__ act, const A* __restrict__ w_down,
     for (int i = threadIdx.x; i < top * ff; i += RE_THREADS) as[i] = act[(size_t)t * top * ff + i];
     __syncthreads();
     const bool vec = ff % 8 == 0 && ((uintptr_t)w_down & 31) == 0;
-    for (int c = blockIdx.y * RE_UNITS + warp; c < min(width, (int)(blockIdx.y + 1) * RE_UNITS);
-         c += RE_THREADS / 32) {
-        float total = 0.f;
+    const int c_end = min(width, (int)(blockIdx.y + 1) * RE_UNITS);
+    for (int c0 = blockIdx.y * RE_UNITS + warp * 4; c0 < c_end; c0 += (RE_THREADS / 32) * 4) {
+        float total[4] = {0.f, 0.f, 0.f, 0.f};
         for (int k = 0; k < top; ++k) {
             const int e = chosen[(size_t)t * top + k];
-            const A* wrow = w_down + ((size_t)e * width + c) * ff;
-            float s = 0.f;
+            const A* wexp = w_down + (size_t)e * width * ff;
+            float s4[4] = {0.f, 0.f, 0.f, 0.f};
             if (vec) {
                 for (int c2 = lane; c2 < (ff >> 3); c2 += 32) {
-                    float a8[8];
-                    load8(wrow + 8 * c2, a8);
+                    float a8[4][8];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) s = fmaf(a8[i], as[k * ff + 8 * c2 + i], s);
+                    for (int q = 0; q < 4; ++q)
+                        load8(wexp + (size_t)min(c0 + q, width - 1) * ff + 8 * c2, a8[q]);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float av = as[k * ff + 8 * c2 + i];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) s4[q] = fmaf(a8[q][i], av, s4[q]);
+                    }
                 }
             } else {
-                for (int j = lane; j < ff; j += 32) s = fmaf(to_float(wrow[j]), as[k * ff + j], s);
+                for (int j = lane; j < ff; j += 32) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        s4[q] = fmaf(to_float(wexp[(size_t)min(c0 + q, width - 1) * ff + j]), as[k * ff + j], s4[q]);
+                }
             }
-            s = warp_sum(s);
-            total += scale_input ? s : s * weight[(size_t)t * top + k];
+            const float wk = scale_input ? 1.f : weight[(size_t)t * top + k];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) total[q] += warp_sum(s4[q]) * wk;
         }
         if (lane == 0) {
-            if (add != nullptr) total += to_float(add[(size_t)t * width + c]);
-            out[(size_t)t * width + c] = from_float<A>(total);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int c = c0 + q;
+                if (c < c_end) {
+                    float v = total[q];
+                    if (add != nullptr) v += to_float(add[(size_t)t * width + c]);
+                    out[(size_t)t * width + c] = from_float<A>(v);
+                }
+            }
         }
     }
 }
