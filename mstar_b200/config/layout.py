@@ -148,8 +148,8 @@ class RoutedExpertsSpec:
     ``top``, plus an optional shared one (``shared_size`` > 0) that every token uses.
 
     Router logits are float.  ``score``: "sigmoid" or "softmax" over all experts.
-    ``renormalize``: the chosen scores are divided by their sum.  ``scale_input``: the
-    weight multiplies the expert's input (True) or its output (False).
+    ``renormalize``: the chosen scores are divided by their sum.  ``scale_input``: True
+    scales what goes into the expert by the weight, False what comes out of it.
     """
 
     kind: str = "routed_experts"

@@ -4,9 +4,9 @@ config.json lists the layers one by one: ``layers[i] = {"type", "mixer": {...}, 
 {...} | null}``; beside it stand ``width``, ``vocab`` and ``norm.eps``.  A layer's mixer is
 a matrix memory (types "mlstm" and "mlstm_2", the same cell under two names) or a
 windowed latent attention ("latent_attention"); its feed-forward is dense, routed experts,
-or absent.  Every layer is a sandwich block: a norm before and after each sublayer, all
-with weights stored around zero.  Nothing has a size default: what config.json does not
-give is an error, and every size may differ from layer to layer.
+or absent.  Every layer is a sandwich block: a norm before and after each sublayer, each
+with its weight stored as an offset from one.  Nothing has a size default: what config.json
+does not give is an error, and every size may differ from layer to layer.
 """
 from __future__ import annotations
 
