@@ -377,6 +377,206 @@ latent_attention_mma_kernel(const float* __restrict__ q_abs, const bf16* __restr
     }
 }
 
+// Scores and the weighted sum on the tensor cores, for a bfloat16 cache with D a multiple of 16
+// and a rank that is a multiple of 32.  A block takes one token and up to 16 heads (the rows of
+// the m16n8k16 tiles).  The probabilities are float; for the product with the latents each is
+// written as the sum of three bfloat16 numbers (head, middle, tail: 3 x 8 bits hold a float's
+// 24-bit mantissa exactly), and the three products are added in the float accumulator, so the
+// weighted sum is that of the float probabilities.  Warp w owns the columns
+// [w rank/4, (w+1) rank/4) of the output: NB tiles of 8 columns, 4 floats a thread each.
+template <int NB>
+__global__ void __launch_bounds__(LAT_THREADS)
+latent_attention_tc_kernel(const float* __restrict__ q_abs, const bf16* __restrict__ q_rot,
+                           float* __restrict__ out, float* __restrict__ part_acc,
+                           float* __restrict__ part_ml, const bf16* __restrict__ cache,
+                           const int* __restrict__ block_table, const int* __restrict__ token_req,
+                           const int* __restrict__ cache_pos, LatentArgs a) {
+    constexpr int PK = LAT_TILE + 8;                   // row stride of the probability tiles
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int t = blockIdx.x, h0 = blockIdx.y * a.group, split = blockIdx.z;
+    const int G = min(a.group, a.heads - h0);
+    const int D = a.rank + a.rot, DP = D + 8;
+    bf16* qh = reinterpret_cast<bf16*>(smem_raw);      // [16][DP] head of the query
+    bf16* ql = qh + 16 * DP;                           // [16][DP] remainder
+    bf16* tile = ql + 16 * DP;                         // [TILE][DP]
+    bf16* ph = tile + LAT_TILE * DP;                   // [3][16][PK] probabilities: head, middle, tail
+    float* sc = reinterpret_cast<float*>(ph + 3 * 16 * PK);   // [TILE][16]
+    float* m_s = sc + LAT_TILE * 16;
+    float* l_s = m_s + 16;
+    float* alpha_s = l_s + 16;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const unsigned long long waited = pdl_wait();
+    q_abs = pdl_after(q_abs, waited);
+    q_rot = pdl_after(q_rot, waited);
+    cache = pdl_after(cache, waited);
+
+    const int hi = cache_pos[t] + 1;
+    const int lo = (a.window > 0 && hi > a.window) ? hi - a.window : 0;
+    const int* bt = block_table + (size_t)token_req[t] * a.bt_stride;
+
+    for (int i = tid; i < 16 * D; i += LAT_THREADS) {
+        const int g = i / D, d = i - g * D;
+        float v = 0.f;
+        if (g < G)
+            v = d < a.rank ? q_abs[((size_t)t * a.heads + h0 + g) * a.rank + d]
+                           : to_float(q_rot[(size_t)t * a.ldq + (size_t)(h0 + g) * a.q_head + (d - a.rank)]);
+        const bf16 head = __float2bfloat16_rn(v);
+        qh[g * DP + d] = head;
+        ql[g * DP + d] = __float2bfloat16_rn(v - __bfloat162float(head));
+    }
+    for (int i = tid; i < 3 * 16 * PK; i += LAT_THREADS) ph[i] = __float2bfloat16_rn(0.f);
+    for (int i = tid; i < 16; i += LAT_THREADS) {
+        m_s[i] = -INFINITY;
+        l_s[i] = 0.f;
+        alpha_s[i] = 1.f;
+    }
+    float acc[NB][4];
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[nb][i] = 0.f;
+    const int chunks = D >> 3;
+    const int nb_warp = a.rank >> 5;                   // tiles of 8 columns a warp (<= NB)
+    const int col_warp = warp * nb_warp * 8;
+    const int g = lane >> 2, t4 = lane & 3;
+
+    for (int base = lo + split * LAT_TILE; base < hi; base += a.splits * LAT_TILE) {
+        __syncthreads();                               // the tile of the round before is done with
+        // a warp per row (the row's address once), lanes over its 16-byte chunks
+        for (int j = warp; j < LAT_TILE; j += LAT_THREADS / 32) {
+            const int key = base + j;
+            const bool seen = key < hi;
+            const bf16* src = cache;
+            if (seen) src = cache + ((size_t)bt[key / a.page_size] * a.page_size + key % a.page_size) * D;
+            for (int c = lane; c < chunks; c += 32)
+                cp_async_16(smem_u32(tile + j * DP + c * 8), seen ? src + c * 8 : cache, seen ? 16 : 0);
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+        __syncthreads();
+        // scores: warp w takes keys 8w .. 8w+7 and all 16 head rows
+        {
+            // four chains of products (head / remainder of the query, even / odd k-step), so
+            // that a product does not wait for the one before it
+            float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+            float sc2[4] = {0.f, 0.f, 0.f, 0.f}, sd[4] = {0.f, 0.f, 0.f, 0.f};
+            const int arow = lane & 15, acol = (lane >> 4) * 8;
+            const int brow = warp * 8 + (lane & 7), bcol = ((lane >> 3) & 1) * 8;
+            for (int k0 = 0; k0 < D; k0 += 32) {
+                uint32_t ah[4], al[4], b0, b1;
+                ldmatrix_x4(ah, smem_u32(qh + arow * DP + k0 + acol));
+                ldmatrix_x4(al, smem_u32(ql + arow * DP + k0 + acol));
+                asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n"
+                             : "=r"(b0), "=r"(b1)
+                             : "r"(smem_u32(tile + brow * DP + k0 + bcol)));
+                mma_bf16_16816(sa, ah, b0, b1);
+                mma_bf16_16816(sb, al, b0, b1);
+                if (k0 + 16 < D) {
+                    ldmatrix_x4(ah, smem_u32(qh + arow * DP + k0 + 16 + acol));
+                    ldmatrix_x4(al, smem_u32(ql + arow * DP + k0 + 16 + acol));
+                    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n"
+                                 : "=r"(b0), "=r"(b1)
+                                 : "r"(smem_u32(tile + brow * DP + k0 + 16 + bcol)));
+                    mma_bf16_16816(sc2, ah, b0, b1);
+                    mma_bf16_16816(sd, al, b0, b1);
+                }
+            }
+            float s4[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) s4[i] = (sa[i] + sc2[i]) + (sb[i] + sd[i]);
+            const int j0 = warp * 8 + 2 * t4;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int head = g + 8 * half;
+                sc[j0 * 16 + head] = base + j0 < hi ? s4[2 * half] * a.scale : -INFINITY;
+                sc[(j0 + 1) * 16 + head] = base + j0 + 1 < hi ? s4[2 * half + 1] * a.scale : -INFINITY;
+            }
+        }
+        __syncthreads();
+        // softmax of the tile, a warp per head; the probabilities in three bfloat16 parts
+        for (int hd = warp; hd < G; hd += LAT_THREADS / 32) {
+            const float sv = sc[lane * 16 + hd];
+            const float m_old = m_s[hd];
+            const float m_new = fmaxf(m_old, warp_max(sv));  // key `base` is always valid
+            const float p = expf(sv - m_new);
+            const float psum = warp_sum(p);
+            const bf16 p0 = __float2bfloat16_rn(p);
+            const float r1 = p - __bfloat162float(p0);
+            const bf16 p1 = __float2bfloat16_rn(r1);
+            const bf16 p2 = __float2bfloat16_rn(r1 - __bfloat162float(p1));
+            ph[hd * PK + lane] = p0;
+            ph[(16 + hd) * PK + lane] = p1;
+            ph[(32 + hd) * PK + lane] = p2;
+            if (lane == 0) {
+                const float al = expf(m_old - m_new);
+                alpha_s[hd] = al;
+                l_s[hd] = l_s[hd] * al + psum;
+                m_s[hd] = m_new;
+            }
+        }
+        __syncthreads();
+        // weighted sum: acc = alpha acc + P V, V the first `rank` features of the rows
+        {
+            const float a_lo = alpha_s[g], a_hi = alpha_s[g + 8];
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) {
+                acc[nb][0] *= a_lo; acc[nb][1] *= a_lo;
+                acc[nb][2] *= a_hi; acc[nb][3] *= a_hi;
+            }
+            const int arow = lane & 15, acol = (lane >> 4) * 8;
+            const int vrow = (lane & 7) + ((lane >> 3) & 1) * 8, vcol = (lane >> 4) * 8;
+#pragma unroll
+            for (int k0 = 0; k0 < LAT_TILE; k0 += 16) {
+                uint32_t p0[4], p1[4], p2[4];
+                ldmatrix_x4(p0, smem_u32(ph + arow * PK + k0 + acol));
+                ldmatrix_x4(p1, smem_u32(ph + (16 + arow) * PK + k0 + acol));
+                ldmatrix_x4(p2, smem_u32(ph + (32 + arow) * PK + k0 + acol));
+#pragma unroll
+                for (int nb = 0; nb < NB; nb += 2) {
+                    if (nb < nb_warp) {
+                        uint32_t v[4];
+                        ldmatrix_x4_trans(v, smem_u32(tile + (k0 + vrow) * DP + col_warp + nb * 8 + vcol));
+                        mma_bf16_16816(acc[nb], p2, v[0], v[1]);
+                        mma_bf16_16816(acc[nb], p1, v[0], v[1]);
+                        mma_bf16_16816(acc[nb], p0, v[0], v[1]);
+                        if (nb + 1 < NB) {
+                            mma_bf16_16816(acc[nb + 1 < NB ? nb + 1 : nb], p2, v[2], v[3]);
+                            mma_bf16_16816(acc[nb + 1 < NB ? nb + 1 : nb], p1, v[2], v[3]);
+                            mma_bf16_16816(acc[nb + 1 < NB ? nb + 1 : nb], p0, v[2], v[3]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+        if (nb >= nb_warp) continue;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int hd = g + 8 * half;
+            if (hd >= G) continue;
+            const size_t th = (size_t)t * a.heads + h0 + hd;
+            const int d = col_warp + nb * 8 + 2 * t4;
+            const float v0 = acc[nb][2 * half], v1 = acc[nb][2 * half + 1];
+            if (a.splits == 1) {
+                const float inv = 1.f / l_s[hd];
+                out[th * a.rank + d] = v0 * inv;
+                out[th * a.rank + d + 1] = v1 * inv;
+            } else {
+                part_acc[(th * a.splits + split) * a.rank + d] = v0;
+                part_acc[(th * a.splits + split) * a.rank + d + 1] = v1;
+                if (d == 0) {
+                    part_ml[(th * a.splits + split) * 2] = m_s[hd];
+                    part_ml[(th * a.splits + split) * 2 + 1] = l_s[hd];
+                }
+            }
+        }
+    }
+}
+
 // out[t, h, :] = sum_s exp(m_s - M) acc_s / sum_s exp(m_s - M) l_s, in the order of the splits.
 // A split that saw no key has l = 0 and m = -inf and adds nothing.
 __global__ void latent_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
@@ -453,6 +653,41 @@ MSTAR_API int mstar_latent_attention(const float* q_abs, const void* q_rot, int 
     if (cores_only < 0) {
         const char* e = getenv("MSTAR_LATENT_ATTENTION");
         cores_only = (e != nullptr && e[0] == 'c') ? 1 : 0;
+    }
+    // ... and the weighted sum as well where the rank is a multiple of 32 (a block then takes
+    // up to 16 heads whatever `group` asks for; MSTAR_LATENT_ATTENTION=scores keeps the sum on
+    // the CUDA cores)
+    static int scores_only = -1;
+    if (scores_only < 0) {
+        const char* e = getenv("MSTAR_LATENT_ATTENTION");
+        scores_only = (e != nullptr && e[0] == 's') ? 1 : 0;
+    }
+    const size_t smem_tc = sizeof(bf16) * ((size_t)(32 + LAT_TILE) * (D + 8) + 3 * 16 * (LAT_TILE + 8)) +
+                           sizeof(float) * (LAT_TILE * 16 + 3 * 16);
+    if (act_dtype == MSTAR_BF16 && D % 16 == 0 && rank % 32 == 0 && ((uintptr_t)cache & 15) == 0 &&
+        !cores_only && !scores_only && smem_tc <= 200 * 1024) {
+        const int tc_group = heads < 16 ? heads : 16;
+        LatentArgs b = a;
+        b.group = tc_group;
+        dim3 tc_grid(num_tokens, (heads + tc_group - 1) / tc_group, splits);
+#define GO_TC(NB)                                                                                 \
+    {                                                                                             \
+        static size_t configured = 0;                                                             \
+        if (smem_tc > 48 * 1024 && smem_tc > configured) {                                        \
+            cudaFuncSetAttribute(latent_attention_tc_kernel<NB>,                                  \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_tc);      \
+            configured = smem_tc;                                                                 \
+        }                                                                                         \
+        mstar_launch((latent_attention_tc_kernel<NB>), tc_grid, dim3(LAT_THREADS), smem_tc, s,    \
+                     q_abs, (const bf16*)q_rot, out, part_acc, part_ml, (const bf16*)cache,       \
+                     block_table, token_req, cache_pos, b);                                       \
+    }
+        if (rank <= 128) GO_TC(4) else if (rank <= 256) GO_TC(8) else if (rank <= 512) GO_TC(16) else GO_TC(32)
+#undef GO_TC
+        if (splits > 1)
+            mstar_launch(latent_merge_kernel, dim3(num_tokens * heads), dim3(128), 0, s,
+                         (const float*)part_acc, (const float*)part_ml, out, rank, splits);
+        return launch_status();
     }
     const size_t smem_mma = sizeof(bf16) * (size_t)(32 + LAT_TILE) * (D + 8) +
                             sizeof(float) * ((size_t)gp * LAT_TILE + 3 * (size_t)gp);

@@ -816,17 +816,19 @@ def latent_fill(proj: torch.Tensor, dkv_offset: int, norm_weight: torch.Tensor, 
 
 def latent_attention_plan(tokens: int, heads: int, rank: int, max_keys: int,
                           sms: int | None = None) -> tuple:
-    """(heads per block, splits of a token's keys) for the latent attention kernel: with many
-    tokens a block takes as many heads as its registers hold (they share the rows it loads)
-    and all keys; with few, smaller groups and shared keys until there are some two blocks
-    per SM, a split keeping at least two tiles of 32 keys."""
+    """(heads per block, splits of a token's keys) for the latent attention kernels.  The
+    tensor-core kernel takes up to 16 heads a block whatever the first number says; the
+    CUDA-core kernels take as many heads as a thread's 32 sums allow (they share the rows a
+    block loads), fewer when tokens are few.  With few tokens a token's keys are shared among
+    blocks until there are some two blocks per SM, a split keeping at least two tiles of 32
+    keys."""
     if sms is None:
         sms = num_sms()
     group = max(1, min(heads, 16 if rank <= 256 else (8 if rank <= 512 else 4)))
     want = 2 * sms
     while group > 4 and tokens * -(-heads // group) < want:
         group = max(4, group // 2)
-    blocks = tokens * -(-heads // group)
+    blocks = tokens * -(-heads // 16)
     tiles = max(1, -(-max_keys // 32))
     splits = max(1, min(want // max(blocks, 1), tiles // 2, 32))
     return group, splits
