@@ -136,22 +136,30 @@ def attention_part(m, width, dtype, seed):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("window,rot_dims,page", [(11, 8, 4), (9, 4, 8), (None, 8, 16), (1, 2, 4)])
-def test_latent_attention_alone(dtype, window, rot_dims, page):
+@pytest.mark.parametrize("window,rot_dims,page,heads,rank,rot",
+                         [(11, 8, 4, 3, 40, 8), (9, 4, 8, 3, 40, 8), (None, 8, 16, 3, 40, 8),
+                          (1, 2, 4, 3, 40, 8),
+                          # rows of whole k-steps and ranks of whole column tiles: in bfloat16 both
+                          # products run on the tensor cores (18 heads: two blocks a token; rank 96:
+                          # an odd number of column tiles a warp)
+                          (13, 16, 8, 5, 64, 16), (37, 8, 16, 18, 96, 16), (None, 16, 4, 2, 32, 16),
+                          # rows of 28 features: no 16-byte rows in bfloat16
+                          (6, 4, 8, 2, 24, 4)])
+def test_latent_attention_alone(dtype, window, rot_dims, page, heads, rank, rot):
     """The attention mixer alone with scores so sharp that one key carries a query's weight:
     a key that a window of the wrong size would take in or leave out, at page borders or far
     back, changes the output by its whole value.  Portions down to two tokens and single
     tokens; pages scattered over the pool."""
     from mstar_b200.parts import LayerCache
 
-    m = U.attention_layer(heads=3, dim=24, rot_dim=8, rot_dims=rot_dims, vdim=20, rank=40,
+    m = U.attention_layer(heads=heads, dim=24, rot_dim=rot, rot_dims=rot_dims, vdim=20, rank=rank,
                           window=window, scale=1.5)["mixer"]
     part, spec, w = attention_part(m, 96, dtype, seed=7)
     T = 70
     x = rnd(T, 96, seed=8)
     want, _ = P.latent_attention_mixer(x.double(), w, "l0.mix.", m, 1e-5, torch.arange(T))
     pages = -(-T // page)
-    kv = torch.full((pages + 3, 1, 1, page, 48), 7.0, dtype=TORCH[dtype], device=DEV)
+    kv = torch.full((pages + 3, 1, 1, page, rank + rot), 7.0, dtype=TORCH[dtype], device=DEV)
     table = (torch.randperm(pages + 3, generator=torch.Generator().manual_seed(1))[:pages]
              .to(torch.int32).to(DEV)[None])
     cache = LayerCache(kv=kv, page_size=page, block_table=table)
