@@ -581,24 +581,31 @@ latent_attention_tc_kernel(const float* __restrict__ q_abs, const bf16* __restri
 // A split that saw no key has l = 0 and m = -inf and adds nothing.
 __global__ void latent_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                     float* __restrict__ out, int rank, int splits) {
+    __shared__ float w_s[32];                  // exp(m_s - M) of every split (at most 32)
+    __shared__ float inv_l;
     const unsigned long long waited = pdl_wait();
     part_acc = pdl_after(part_acc, waited);
     part_ml = pdl_after(part_ml, waited);
     const size_t th = blockIdx.x;
-    float M = -INFINITY;
-    for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[(th * splits + s) * 2]);
-    float L = 0.f;
-    for (int s = 0; s < splits; ++s) {
-        const float m = part_ml[(th * splits + s) * 2];
-        if (m > -INFINITY) L += expf(m - M) * part_ml[(th * splits + s) * 2 + 1];
+    if (threadIdx.x < 32) {
+        const int sp = threadIdx.x;
+        const float m = sp < splits ? part_ml[(th * splits + sp) * 2] : -INFINITY;
+        const float l = sp < splits ? part_ml[(th * splits + sp) * 2 + 1] : 0.f;
+        const float M = warp_max(m);
+        const float w = m > -INFINITY ? expf(m - M) : 0.f;
+        // the sum over the splits in their order, by one lane
+        w_s[sp] = w;
+        const float wl = w * l;
+        float L = 0.f;
+        for (int i = 0; i < splits; ++i) L += __shfl_sync(0xffffffffu, wl, i);
+        if (sp == 0) inv_l = 1.f / L;
     }
+    __syncthreads();
     for (int d = threadIdx.x; d < rank; d += blockDim.x) {
         float sum = 0.f;
-        for (int s = 0; s < splits; ++s) {
-            const float m = part_ml[(th * splits + s) * 2];
-            if (m > -INFINITY) sum = fmaf(expf(m - M), part_acc[(th * splits + s) * rank + d], sum);
-        }
-        out[th * rank + d] = sum / L;
+        for (int sp = 0; sp < splits; ++sp)
+            sum = fmaf(w_s[sp], part_acc[(th * splits + sp) * rank + d], sum);
+        out[th * rank + d] = sum * inv_l;
     }
 }
 
@@ -637,6 +644,7 @@ MSTAR_API int mstar_latent_attention(const float* q_abs, const void* q_rot, int 
     if (group > heads) group = heads;
     const int gp = group <= 4 ? 4 : (group <= 8 ? 8 : 16);
     if (splits < 1) splits = 1;
+    if (splits > 32) return -1;               // the merge kernel takes up to 32
     if (splits > 1 && scratch == nullptr) return -1;
     const int D = rank + rot;
     const size_t smem = sizeof(float) * ((size_t)gp * D + (size_t)LAT_TILE * (D + 1) +

@@ -285,24 +285,26 @@ MSTAR_API int mstar_matrix_memory_scan(const void* qkv, int act_dtype, int ld, i
 }
 
 // out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * weight[h, :] * sigmoid(gate[t, h, :]); one warp
-// per (token, head), float sums.
-template <typename A>
+// per (token, head) where there are many, a block of four warps where there are few; float sums.
+template <typename A, bool BLOCK>
 __global__ void head_norm_gate_kernel(const float* __restrict__ o, const A* __restrict__ gate, int ldg,
                                       const float* __restrict__ weight, A* __restrict__ out,
                                       int pairs, int heads, int vdim, float eps) {
+    __shared__ float scratch[32];
     const unsigned long long waited = pdl_wait();
     o = pdl_after(o, waited);
     gate = pdl_after(gate, waited);
-    const int pair = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int pair = BLOCK ? blockIdx.x : blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (pair >= pairs) return;
-    const int lane = threadIdx.x & 31;
+    const int first = BLOCK ? threadIdx.x : (threadIdx.x & 31), step = BLOCK ? blockDim.x : 32;
     const int t = pair / heads, h = pair - t * heads;
     const float* row = o + (size_t)pair * vdim;
     float ss = 0.f;
-    for (int j = lane; j < vdim; j += 32) ss = fmaf(row[j], row[j], ss);
-    const float inv = rsqrtf(warp_sum(ss) / (float)vdim + eps);
+    for (int j = first; j < vdim; j += step) ss = fmaf(row[j], row[j], ss);
+    const float total = BLOCK ? block_sum(ss, scratch) : warp_sum(ss);
+    const float inv = rsqrtf(total / (float)vdim + eps);
     const A* g = gate + (size_t)t * ldg + (size_t)h * vdim;
-    for (int j = lane; j < vdim; j += 32) {
+    for (int j = first; j < vdim; j += step) {
         const float gv = to_float(g[j]);
         out[(size_t)pair * vdim + j] =
             from_float<A>(row[j] * inv * weight[(size_t)h * vdim + j] / (1.f + expf(-gv)));
@@ -315,12 +317,16 @@ MSTAR_API int mstar_head_norm_gate(const float* o, const void* gate, int ldg, co
     if (tokens <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const int pairs = tokens * heads, warps = 4;
-    dim3 grid((pairs + warps - 1) / warps);
-    if (act_dtype == MSTAR_F32)
-        mstar_launch((head_norm_gate_kernel<float>), grid, dim3(32 * warps), 0, s, o, (const float*)gate,
-                     ldg, weight, (float*)out, pairs, heads, vdim, eps);
-    else
-        mstar_launch((head_norm_gate_kernel<bf16>), grid, dim3(32 * warps), 0, s, o, (const bf16*)gate,
-                     ldg, weight, (bf16*)out, pairs, heads, vdim, eps);
+    const bool few = pairs < 4 * device_sm_count();
+    dim3 grid(few ? pairs : (pairs + warps - 1) / warps);
+#define LAUNCH(A, B)                                                                              \
+    mstar_launch((head_norm_gate_kernel<A, B>), grid, dim3(32 * warps), 0, s, o, (const A*)gate, ldg, \
+                 weight, (A*)out, pairs, heads, vdim, eps)
+    if (act_dtype == MSTAR_F32) {
+        if (few) LAUNCH(float, true); else LAUNCH(float, false);
+    } else {
+        if (few) LAUNCH(bf16, true); else LAUNCH(bf16, false);
+    }
+#undef LAUNCH
     return launch_status();
 }

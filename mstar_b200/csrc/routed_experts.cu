@@ -18,46 +18,70 @@
 #include "common.cuh"
 
 // ------------------------------------------------------------------ choice
+// A warp per token: lane l holds the logits of experts l, l + 32, ... (up to 32 of them, so up
+// to 1,024 experts); the largest logit not chosen yet is found `top` times by a warp-wide
+// comparison of (value, index), the lower index winning a tie.  Scores are monotone in the
+// logits, so the choice is made on the logits.
+#define RT_PER_LANE 32
+
 __global__ void route_topk_kernel(const float* __restrict__ logits, int* __restrict__ chosen,
                                   float* __restrict__ weight, int tokens, int experts, int top,
                                   int softmax, int renormalize) {
     logits = pdl_after(logits, pdl_wait());
-    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (t >= tokens) return;
     const float* z = logits + (size_t)t * experts;
     float zmax = -INFINITY, denom = 1.f;
     if (softmax) {
-        for (int e = 0; e < experts; ++e) zmax = fmaxf(zmax, z[e]);
+        for (int e = lane; e < experts; e += 32) zmax = fmaxf(zmax, z[e]);
+        zmax = warp_max(zmax);
         denom = 0.f;
-        for (int e = 0; e < experts; ++e) denom += expf(z[e] - zmax);
+        for (int e = lane; e < experts; e += 32) denom += expf(z[e] - zmax);
+        denom = warp_sum(denom);
     }
+    unsigned taken = 0u;                       // bit i: expert lane + 32 i is chosen
     float total = 0.f;
     for (int k = 0; k < top; ++k) {
-        // the largest logit not chosen yet: scores are monotone in the logits
-        int best = -1;
         float bz = -INFINITY;
-        for (int e = 0; e < experts; ++e) {
-            bool taken = false;
-            for (int j = 0; j < k; ++j) taken |= chosen[(size_t)t * top + j] == e;
-            if (!taken && (best < 0 || z[e] > bz)) {
-                best = e;
-                bz = z[e];
+        int be = 0x7fffffff;
+        for (int i = 0; i < RT_PER_LANE; ++i) {
+            const int e = lane + 32 * i;
+            if (e >= experts) break;
+            if (!((taken >> i) & 1u)) {
+                const float v = z[e];
+                if (be == 0x7fffffff || v > bz) {
+                    bz = v;
+                    be = e;
+                }
             }
         }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float oz = __shfl_xor_sync(0xffffffffu, bz, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+            if (oe != 0x7fffffff && (be == 0x7fffffff || oz > bz || (oz == bz && oe < be))) {
+                bz = oz;
+                be = oe;
+            }
+        }
+        if ((be & 31) == lane) taken |= 1u << (be >> 5);
         const float s = softmax ? expf(bz - zmax) / denom : 1.f / (1.f + expf(-bz));
-        chosen[(size_t)t * top + k] = best;
-        weight[(size_t)t * top + k] = s;
         total += s;
+        if (lane == 0) {
+            chosen[(size_t)t * top + k] = be;
+            weight[(size_t)t * top + k] = s;
+        }
     }
-    if (renormalize)
+    if (renormalize && lane == 0)
         for (int k = 0; k < top; ++k) weight[(size_t)t * top + k] /= total;
 }
 
 MSTAR_API int mstar_route_topk(const float* logits, int* chosen, float* weight, int tokens,
                                int experts, int top, int softmax, int renormalize, void* stream) {
     if (tokens <= 0) return 0;
-    if (experts <= 0 || top <= 0 || top > experts) return -1;
-    mstar_launch(route_topk_kernel, dim3((tokens + 127) / 128), dim3(128), 0, (cudaStream_t)stream,
+    if (experts <= 0 || top <= 0 || top > experts || experts > 32 * RT_PER_LANE) return -1;
+    mstar_launch(route_topk_kernel, dim3((tokens + 3) / 4), dim3(128), 0, (cudaStream_t)stream,
                  logits, chosen, weight, tokens, experts, top, softmax, renormalize);
     return launch_status();
 }

@@ -322,14 +322,10 @@ class Stepper:
         sources = None
         if pending:
             sources = [pending.get(i, -1) for i in range(len(entries))]
-        saved = None
-        if self.storage.has_state:
-            saved = self.storage.snapshot_state([self.manager.slot(r) for r in requests])
-        try:
-            logits = graph.run(requests, [e.tokens[0] for e in entries], sources)
-        except BaseException:
-            self.storage.restore_state(saved)
-            raise
+        # no copy of the state rows here: a replay runs no Python of the parts, so nothing can
+        # raise between the first and the last kernel of the step; what can raise (filling the
+        # index buffer) does so before anything is launched
+        logits = graph.run(requests, [e.tokens[0] for e in entries], sources)
         self.last_h2d_bytes = graph.size * 4
         for request in requests:
             self.manager.commit(request, 1)
