@@ -247,7 +247,7 @@ MSTAR_API int mstar_experts_by_row(const void* x, const void* w_gate_up, const v
 // For many rows (prompt portions) the rows are sorted by expert, and every expert's rows go
 // through its matrices as tiles of a tensor-core GEMM (bfloat16 mma.sync, float sums):
 //   1. experts_sort: counting sort of the rows (token x choice) by expert; the list of row
-//      tiles (expert, first sorted row), one per 64 rows of a group.
+//      tiles (expert, first sorted row), one per 64 (or 128) rows of a group.
 //   2. grouped GEMM, gated: act[p] = silu(w G) * (w U), G and U the products of the gathered
 //      token rows with the expert's gate and up rows (bfloat16 out, sorted order).
 //   3. grouped GEMM, plain: y[p] = act[p] W_down[e]^T (float out, sorted order).
@@ -257,14 +257,12 @@ MSTAR_API int mstar_experts_by_row(const void* x, const void* w_gate_up, const v
 // nothing, so the order inside a group need not be stable.
 #include "mma_util.cuh"
 
-#define GG_BM 64
 #define GG_BN 64
 #define GG_BK 32
 #define GG_LD 40          // bf16 elements between rows of a shared tile (80 bytes: no bank conflicts)
-#define GG_THREADS 128
 #define GG_STAGES 3
 
-__global__ void experts_sort_kernel(const int* __restrict__ chosen, int rows, int experts,
+__global__ void experts_sort_kernel(const int* __restrict__ chosen, int rows, int experts, int tile_rows,
                                     int* __restrict__ order, int* __restrict__ pos,
                                     int* __restrict__ offsets, int* __restrict__ tile_expert,
                                     int* __restrict__ tile_first, int* __restrict__ num_tiles) {
@@ -281,7 +279,7 @@ __global__ void experts_sort_kernel(const int* __restrict__ chosen, int rows, in
         for (int e = 0; e < experts; ++e) {
             offsets[e] = at;
             cursor[e] = at;
-            for (int p = at; p < at + counts[e]; p += GG_BM) {
+            for (int p = at; p < at + counts[e]; p += tile_rows) {
                 tile_expert[tiles] = e;
                 tile_first[tiles] = p;
                 ++tiles;
@@ -299,20 +297,23 @@ __global__ void experts_sort_kernel(const int* __restrict__ chosen, int rows, in
     }
 }
 
-// C tile [64 x 64] of one expert's group.  GATED: A rows are x[order[p] / top], B rows are
+// C tile [GG_BM x 64] of one expert's group (a warp per 32 x 32 of it).  GATED: A rows are x[order[p] / top], B rows are
 // the expert's gate rows n0.. and up rows ff + n0..; out = silu(w G) * (w U) as bfloat16.
 // Plain: A rows are act[p], B rows the expert's down rows n0..; out float.
-template <bool GATED>
-__global__ void __launch_bounds__(GG_THREADS)
+template <bool GATED, int GG_BM>
+__global__ void __launch_bounds__(GG_BM * 2)
 grouped_gemm_kernel(const bf16* __restrict__ a_src, const bf16* __restrict__ w, void* __restrict__ out,
                     const int* __restrict__ order, const float* __restrict__ weight,
                     const int* __restrict__ offsets, const int* __restrict__ tile_expert,
                     const int* __restrict__ tile_first, const int* __restrict__ num_tiles,
                     int N, int K, int top, int scale_input) {
     constexpr int BROWS = GATED ? 2 * GG_BN : GG_BN;
-    __shared__ __align__(16) bf16 As[GG_STAGES][GG_BM * GG_LD];
-    __shared__ __align__(16) bf16 Bs[GG_STAGES][BROWS * GG_LD];
-    __shared__ int src_row[GG_BM];
+    constexpr int GG_THREADS = GG_BM * 2;             // a warp per 32 x 32 of the tile
+    extern __shared__ __align__(16) unsigned char gg_smem[];
+    bf16 (*As)[GG_BM * GG_LD] = reinterpret_cast<bf16 (*)[GG_BM * GG_LD]>(gg_smem);
+    bf16 (*Bs)[BROWS * GG_LD] = reinterpret_cast<bf16 (*)[BROWS * GG_LD]>(
+        gg_smem + sizeof(bf16) * GG_STAGES * GG_BM * GG_LD);
+    int* src_row = reinterpret_cast<int*>(gg_smem + sizeof(bf16) * GG_STAGES * (GG_BM + BROWS) * GG_LD);
 
     const unsigned long long waited = pdl_wait();
     a_src = pdl_after(a_src, waited);
@@ -461,21 +462,44 @@ MSTAR_API int mstar_experts_grouped(const void* x, const void* w_gate_up, const 
     if (width % 8 != 0 || ff % 8 != 0 || experts <= 0 || experts > 1024 || top <= 0) return -1;
     cudaStream_t s = (cudaStream_t)stream;
     const int rows = tokens * top;
-    const int max_tiles = rows / GG_BM + experts;
+    // tiles of 128 rows where an expert's group fills them on average, else of 64
+    const int bm = rows / experts >= 128 ? 128 : 64;
+    const int max_tiles = rows / bm + experts;
     int* order = ints;
     int* pos = order + rows;
     int* offsets = pos + rows;
     int* num_tiles = offsets + experts + 1;
     int* tile_expert = num_tiles + 1;
-    int* tile_first = tile_expert + max_tiles;
+    int* tile_first = tile_expert + (rows / 64 + experts);
     mstar_launch(experts_sort_kernel, dim3(1), dim3(1024), sizeof(int) * 2 * experts, s, chosen, rows,
-                 experts, order, pos, offsets, tile_expert, tile_first, num_tiles);
-    mstar_launch((grouped_gemm_kernel<true>), dim3((ff + GG_BN - 1) / GG_BN, max_tiles), dim3(GG_THREADS),
-                 0, s, (const bf16*)x, (const bf16*)w_gate_up, act, order, weight, offsets, tile_expert,
-                 tile_first, num_tiles, ff, width, top, scale_input);
-    mstar_launch((grouped_gemm_kernel<false>), dim3((width + GG_BN - 1) / GG_BN, max_tiles),
-                 dim3(GG_THREADS), 0, s, (const bf16*)act, (const bf16*)w_down, (void*)y, order, weight,
-                 offsets, tile_expert, tile_first, num_tiles, width, ff, top, scale_input);
+                 experts, bm, order, pos, offsets, tile_expert, tile_first, num_tiles);
+#define GG_SMEM(BM, BROWS) (sizeof(bf16) * GG_STAGES * ((BM) + (BROWS)) * GG_LD + sizeof(int) * (BM))
+#define GG_GO(GATED, BM, BROWS, GRIDX, ...)                                                       \
+    {                                                                                             \
+        static bool configured = false;                                                           \
+        const size_t bytes = GG_SMEM(BM, BROWS);                                                  \
+        if (!configured && bytes > 48 * 1024) {                                                   \
+            cudaFuncSetAttribute(grouped_gemm_kernel<GATED, BM>,                                  \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);        \
+            configured = true;                                                                    \
+        }                                                                                         \
+        mstar_launch((grouped_gemm_kernel<GATED, BM>), dim3(GRIDX, max_tiles), dim3((BM) * 2), bytes, s, \
+                     __VA_ARGS__);                                                                \
+    }
+    const int gx1 = (ff + GG_BN - 1) / GG_BN, gx2 = (width + GG_BN - 1) / GG_BN;
+    if (bm == 128) {
+        GG_GO(true, 128, 2 * GG_BN, gx1, (const bf16*)x, (const bf16*)w_gate_up, act, order, weight,
+              offsets, tile_expert, tile_first, num_tiles, ff, width, top, scale_input)
+        GG_GO(false, 128, GG_BN, gx2, (const bf16*)act, (const bf16*)w_down, (void*)y, order, weight,
+              offsets, tile_expert, tile_first, num_tiles, width, ff, top, scale_input)
+    } else {
+        GG_GO(true, 64, 2 * GG_BN, gx1, (const bf16*)x, (const bf16*)w_gate_up, act, order, weight,
+              offsets, tile_expert, tile_first, num_tiles, ff, width, top, scale_input)
+        GG_GO(false, 64, GG_BN, gx2, (const bf16*)act, (const bf16*)w_down, (void*)y, order, weight,
+              offsets, tile_expert, tile_first, num_tiles, width, ff, top, scale_input)
+    }
+#undef GG_GO
+#undef GG_SMEM
     mstar_launch((experts_combine_kernel<bf16>), dim3(tokens), dim3(256), 0, s, (const float*)y, pos,
                  weight, (const bf16*)add, (bf16*)out, width, top, scale_input);
     return launch_status();
