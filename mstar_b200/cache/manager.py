@@ -49,11 +49,13 @@ class GroupConfig:
     """One pool of pages shared by the layers (caches) of a group.
 
     window None: all keys are kept until the request ends.  window W: a token
-    sees the last W keys, and pages wholly older than that are released."""
+    sees the last W keys, and pages wholly older than that are released, except those
+    that hold the first ``keep_first`` keys, which every later token sees as well."""
 
     page_size: int
     num_pages: int
     window: Optional[int] = None
+    keep_first: int = 0
 
 
 @dataclass
@@ -84,7 +86,7 @@ def _host_lib():
     i64, i32, vp = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p
     pi32, pi64 = ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int64)
     lib.cm_create.restype = vp
-    lib.cm_create.argtypes = [i32, pi32, pi32, pi32, i32]
+    lib.cm_create.argtypes = [i32, pi32, pi32, pi32, pi32, i32]
     lib.cm_destroy.restype = None
     lib.cm_destroy.argtypes = [vp]
     lib.cm_add_request.restype = i32
@@ -145,13 +147,15 @@ class CacheManager:
         self.groups = list(groups)
         self.num_slots = int(num_slots)
         for g in self.groups:
-            if g.page_size <= 0 or g.num_pages < 0 or (g.window is not None and g.window <= 0):
+            if g.page_size <= 0 or g.num_pages < 0 or (g.window is not None and g.window <= 0) \
+                    or g.keep_first < 0:
                 raise ValueError(f"bad cache group {g}")
         self._lib = _host_lib()
         self._h = self._lib.cm_create(
             len(self.groups), _i32([g.page_size for g in self.groups]),
             _i32([g.num_pages for g in self.groups]),
-            _i32([g.window or 0 for g in self.groups]), self.num_slots)
+            _i32([g.window or 0 for g in self.groups]),
+            _i32([g.keep_first for g in self.groups]), self.num_slots)
         if not self._h:
             raise ValueError("cache manager rejected its configuration")
         self._ids: dict[Hashable, int] = {}

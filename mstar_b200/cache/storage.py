@@ -26,8 +26,9 @@ _STATE_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": 
 
 
 def plan_groups(needs: Sequence[CacheNeed]):
-    """Group caches by the window of their keys.  Returns (windows, group_of):
-    ``windows[g]`` is None or W, ``group_of[cache]`` the group index or None."""
+    """Group caches by which keys have to stay: the window of their keys and the number of
+    first keys kept beside it.  Returns (windows, group_of): ``windows[g]`` is None, W, or
+    (W, keep_first) where first keys are kept; ``group_of[cache]`` the group index or None."""
     windows: list = []
     group_of: list = []
     for need in needs:
@@ -35,10 +36,18 @@ def plan_groups(needs: Sequence[CacheNeed]):
             group_of.append(None)
             continue
         w = need.kv.window
+        if w is not None and need.kv.keep_first:
+            w = (w, need.kv.keep_first)
         if w not in windows:
             windows.append(w)
         group_of.append(windows.index(w))
     return windows, group_of
+
+
+def _kv_shape(kv, pages: int, page_size: int) -> tuple:
+    if kv.v_head_dim is not None and kv.v_head_dim != kv.head_dim:
+        return (pages, kv.num_kv_heads * page_size * (kv.head_dim + kv.v_head_dim))
+    return (pages, kv.planes, kv.num_kv_heads, page_size, kv.head_dim)
 
 
 def group_page_sizes(page_size, num_groups: int) -> list:
@@ -60,7 +69,8 @@ def bytes_per_page(needs: Sequence[CacheNeed], group_of, group: int, page_size: 
     total = 0
     for need, g in zip(needs, group_of):
         if g == group:
-            total += need.kv.planes * need.kv.num_kv_heads * page_size * need.kv.head_dim * item
+            shape = _kv_shape(need.kv, 1, page_size)
+            total += item * int(torch.Size(shape).numel())
     return total
 
 
@@ -80,7 +90,7 @@ class CacheStorage:
             num_pages = [num_pages] * len(self.windows)
         if len(num_pages) != len(self.windows):
             raise ValueError(f"{len(self.windows)} cache groups but {len(num_pages)} page counts")
-        self.group_configs = [GroupConfig(p, int(n), w)
+        self.group_configs = [GroupConfig(p, int(n), *(w if isinstance(w, tuple) else (w,)))
                               for p, n, w in zip(self.page_sizes, num_pages, self.windows)]
         self.manager = CacheManager(self.group_configs, self.num_slots)
         self.kv: list = []
@@ -92,9 +102,8 @@ class CacheStorage:
                 # one page more than the manager hands out: padding entries of
                 # fixed-shape (CUDA graph) batches write their keys there
                 n = self.group_configs[g].num_pages + 1
-                self.kv.append(torch.zeros(
-                    (n, need.kv.planes, need.kv.num_kv_heads, self.page_sizes[g], need.kv.head_dim),
-                    dtype=dtype, device=device))
+                self.kv.append(torch.zeros(_kv_shape(need.kv, n, self.page_sizes[g]), dtype=dtype,
+                                           device=device))
             if need is not None and need.state is not None:
                 self.state.append(torch.zeros((self.num_slots + 1,) + tuple(need.state.shape),
                                               dtype=_STATE_DTYPES[need.state.dtype],

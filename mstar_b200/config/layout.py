@@ -67,6 +67,12 @@ class AttentionSpec:
     see keys ``p-W+1 .. p``.  ``shares_kv``: the layer has no key/value
     projections and reads the cache written by an earlier layer.
     ``scale``: None means ``head_dim ** -0.5``.
+    ``keep_first``: with a window, the keys at positions below it stay visible to every
+    later token (at their true positions).  ``v_head_dim``: size of a value head, None
+    when it equals ``head_dim``.  ``bias``: the q, k and v projections add a bias.
+    ``qk_norm_eps``: not None puts an RMS norm over each query and key head (one weight of
+    ``head_dim`` for the queries and one for the keys, shared by the heads) before the
+    position encoding.
     """
 
     kind: str = "attention"
@@ -78,6 +84,20 @@ class AttentionSpec:
     window: Optional[int] = None
     scale: Optional[float] = None
     shares_kv: bool = False
+    keep_first: int = 0
+    v_head_dim: Optional[int] = None
+    bias: bool = False
+    qk_norm_eps: Optional[float] = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
+
+    @property
+    def plain(self) -> bool:
+        """Whether this is the attention that the kernels of the dense decoder take."""
+        return (not self.keep_first and self.v_head_dim in (None, self.head_dim)
+                and not self.bias and self.qk_norm_eps is None)
 
 
 @dataclass(frozen=True)
@@ -88,6 +108,51 @@ class GatedMLPSpec:
     hidden_size: int = 0
     intermediate_size: int = 0
     activation: str = "silu"
+
+
+@dataclass(frozen=True)
+class MLPSpec:
+    """kind "mlp": ``down(act(up(x)))`` without a gate.  ``activation``: "relu2" (the square
+    of relu), "gelu_tanh" or "silu"."""
+
+    kind: str = "mlp"
+    hidden_size: int = 0
+    intermediate_size: int = 0
+    activation: str = "relu2"
+
+
+@dataclass(frozen=True)
+class SelectiveScanSpec:
+    """kind "selective_scan": the Mamba mixer, a diagonal linear recurrence per channel whose
+    step size and input/output maps depend on the token.
+
+    ``[x | z] = W_in h`` (``inner`` channels each); x passes a causal convolution of ``conv``
+    taps per channel and SiLU; ``[dt_in | B | C] = W_x x`` (``dt_rank``, ``state``, ``state``);
+    ``dt = softplus(W_dt dt_in + b)`` per channel; with ``A = -exp(A_log)``:
+    ``S[c, n] = exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n``, ``y_c = sum_n S[c, n] C_n + D_c x_c``;
+    the output is ``W_o (y * silu(z))``.  S (float) and the convolution's last ``conv - 1``
+    inputs are per-request state.
+    """
+
+    kind: str = "selective_scan"
+    hidden_size: int = 0
+    inner: int = 0
+    state: int = 0
+    dt_rank: int = 0
+    conv: int = 1
+    shares_kv: bool = False
+
+
+@dataclass(frozen=True)
+class ParallelMixerSpec:
+    """kind "parallel": several mixers side by side on the same input; the result is the mean
+    of their outputs, each RMS-normed over the model width with a weight of its own."""
+
+    kind: str = "parallel"
+    hidden_size: int = 0
+    branches: tuple = ()
+    norm_eps: float = 1e-6
+    shares_kv: bool = False
 
 
 @dataclass(frozen=True)
@@ -150,6 +215,11 @@ class RoutedExpertsSpec:
     Router logits are float.  ``score``: "sigmoid" or "softmax" over all experts.
     ``renormalize``: the chosen scores are divided by their sum.  ``scale_input``: True
     scales what goes into the expert by the weight, False what comes out of it.
+    ``gated``: an expert is ``down(act(gate u) * up u)``; False: ``down(act(up u))``.
+    ``choice_bias``: a learned correction per router output is added to the scores for the
+    choice only (the weights use the scores without it).  ``identity_experts``: the router
+    has that many further outputs, standing for experts without tensors whose output is
+    their input.
     """
 
     kind: str = "routed_experts"
@@ -162,6 +232,9 @@ class RoutedExpertsSpec:
     renormalize: bool = False
     scale_input: bool = True
     activation: str = "silu"
+    gated: bool = True
+    choice_bias: bool = False
+    identity_experts: int = 0
 
 
 @dataclass(frozen=True)
@@ -193,6 +266,9 @@ class BlockSpec:
     kind "prenorm": ``h += mixer(norm1(h)); h += ffn(norm2(h))``.
     kind "sandwich": ``h += norm1_post(mixer(norm1(h))); h += norm2_post(ffn(norm2(h)))``;
     ``ffn`` None leaves the second sublayer (and its norms) out.
+    kind "postnorm": ``h += residual_mult * norm1_post(mixer(h)); h += residual_mult *
+    norm2_post(ffn(h))``: the sublayers read the residual itself (``norm1`` and ``norm2`` are
+    None), only their outputs are normed.
     ``mixer`` / ``ffn`` are any registered spec; they may differ from block
     to block within one model.
     """
@@ -200,10 +276,11 @@ class BlockSpec:
     kind: str
     mixer: object
     ffn: object
-    norm1: NormSpec
+    norm1: Optional[NormSpec]
     norm2: Optional[NormSpec]
     norm1_post: Optional[NormSpec] = None
     norm2_post: Optional[NormSpec] = None
+    residual_mult: float = 1.0
 
 
 @dataclass(frozen=True)

@@ -93,3 +93,8 @@ def _register_builtin() -> None:
 
     if "Tifosun" not in _ARCHITECTURES:
         register_architecture("Tifosun", TifosunConfig, tifosun_checkpoint_map)
+    from ..weights.vudivik import vudivik_checkpoint_map
+    from .vudivik import VudivikConfig
+
+    if "Vudivik" not in _ARCHITECTURES:
+        register_architecture("Vudivik", VudivikConfig, vudivik_checkpoint_map)

@@ -1,0 +1,307 @@
+// Grouped-query attention with a sliding window that keeps the first keys of a sequence, a
+// value size of its own, biased projections and an RMS norm per query and key head.
+//
+//   prepare   row = [q: nq*hd | k: nkv*hd | v: nkv*vd] (float, the fused projection) + bias;
+//             every q and k head is divided by its root mean square (eps inside the root)
+//             and scaled by a weight shared by the heads; the first `rot` features of q and
+//             k are rotated (feature i with i + rot/2, angle position * freq[i]); q goes to
+//             a dense [tokens, nq*hd] buffer, k and v into the token's cache page.
+//   attend    the token whose key sits at cache position p sees keys j <= p with
+//             p - j < window or j < keep_first (window 0: every j <= p): the keys
+//             [0, min(keep_first, lo)) and [lo, p], lo = max(0, p - window + 1).  Softmax over
+//             them, scores q.k * scale, float statistics and sums.
+//
+// A cache page is [nkv][page_size][hd] keys followed by [nkv][page_size][vd] values.
+// Norms, angles, scores, probabilities and output sums are float for both activation types.
+#include "common.cuh"
+
+// ------------------------------------------------------------------ prepare
+struct PrepArgs {
+    int nq, nkv, hd, vd, rot, page_size, bt_stride, q_stride_out;
+    float eps;
+    int norm;       // 1: q and k heads are normed
+};
+
+// One block per token.  Sines and cosines of the token's angles are made once (double
+// precision product and sincos) and shared by all heads.
+template <typename A, typename W>
+__global__ void __launch_bounds__(256)
+sink_prepare_kernel(const float* __restrict__ qkv, const W* __restrict__ bias,
+                    const W* __restrict__ q_norm, const W* __restrict__ k_norm,
+                    const double* __restrict__ freq, const int* __restrict__ positions,
+                    const int* __restrict__ cache_pos, const int* __restrict__ token_req,
+                    const int* __restrict__ block_table, A* __restrict__ q_out,
+                    A* __restrict__ kv_cache, PrepArgs a) {
+    extern __shared__ float sm[];
+    const int half = a.rot / 2;
+    float* cs = sm;                            // [half] cosines, [half] sines
+    float* heads = sm + 2 * half;              // [warps][hd]
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = blockDim.x >> 5;
+    const unsigned long long waited = pdl_wait();
+    qkv = pdl_after(qkv, waited);
+    const double pos = (double)positions[t];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        double s, c;
+        sincos(pos * freq[i], &s, &c);
+        cs[i] = (float)c;
+        cs[half + i] = (float)s;
+    }
+    __syncthreads();
+    const int row_len = (a.nq + a.nkv) * a.hd + a.nkv * a.vd;
+    const float* row = qkv + (size_t)t * row_len;
+    const int key = cache_pos[t];
+    const int page = block_table[(size_t)token_req[t] * a.bt_stride + key / a.page_size];
+    const int slot = key % a.page_size;
+    const size_t page_elems = (size_t)a.nkv * a.page_size * (a.hd + a.vd);
+    A* page_base = kv_cache + (size_t)page * page_elems;
+    float* mine = heads + warp * a.hd;
+    for (int h = warp; h < a.nq + 2 * a.nkv; h += nwarps) {
+        if (h >= a.nq + a.nkv) {               // a value head: bias, then the page
+            const int g = h - a.nq - a.nkv;
+            const int off = (a.nq + a.nkv) * a.hd + g * a.vd;
+            A* dst = page_base + (size_t)a.nkv * a.page_size * a.hd +
+                     ((size_t)g * a.page_size + slot) * a.vd;
+            for (int d = lane; d < a.vd; d += 32) {
+                float v = row[off + d];
+                if (bias != nullptr) v += to_float(bias[off + d]);
+                dst[d] = from_float<A>(v);
+            }
+            continue;
+        }
+        const bool is_q = h < a.nq;
+        const int off = h * a.hd;
+        float ss = 0.f;
+        for (int d = lane; d < a.hd; d += 32) {
+            float v = row[off + d];
+            if (bias != nullptr) v += to_float(bias[off + d]);
+            mine[d] = v;
+            ss = fmaf(v, v, ss);
+        }
+        ss = warp_sum(ss);
+        const float inv = a.norm ? rsqrtf(ss / (float)a.hd + a.eps) : 1.f;
+        const W* nw = is_q ? q_norm : k_norm;
+        __syncwarp();
+        if (a.norm)
+            for (int d = lane; d < a.hd; d += 32) mine[d] = mine[d] * inv * to_float(nw[d]);
+        __syncwarp();
+        A* dst = is_q ? q_out + (size_t)t * a.q_stride_out + (size_t)h * a.hd
+                      : page_base + ((size_t)(h - a.nq) * a.page_size + slot) * a.hd;
+        for (int d = lane; d < a.hd; d += 32) {
+            float v = mine[d];
+            if (d < half) {
+                v = mine[d] * cs[d] - mine[d + half] * cs[half + d];
+            } else if (d < a.rot) {
+                const int i = d - half;
+                v = mine[d] * cs[i] + mine[i] * cs[half + i];
+            }
+            dst[d] = from_float<A>(v);
+        }
+        __syncwarp();
+    }
+}
+
+MSTAR_API int mstar_sink_prepare(const float* qkv, const void* bias, const void* q_norm,
+                                 const void* k_norm, int weight_dtype, const double* freq,
+                                 const int* positions, const int* cache_pos, const int* token_req,
+                                 const int* block_table, int bt_stride, void* q_out,
+                                 void* kv_cache, int act_dtype, int tokens, int nq, int nkv, int hd,
+                                 int vd, int rot, int page_size, float eps, int norm, void* stream) {
+    if (tokens <= 0) return 0;
+    if (hd <= 0 || vd <= 0 || rot < 0 || rot > hd || (rot & 1) || nq <= 0 || nkv <= 0) return -1;
+    const int threads = 256;
+    const size_t smem = sizeof(float) * ((size_t)rot + (size_t)(threads / 32) * hd);
+    if (smem > 48 * 1024) return -1;
+    PrepArgs a{nq, nkv, hd, vd, rot, page_size, bt_stride, nq * hd, eps, norm};
+    cudaStream_t s = (cudaStream_t)stream;
+#define GO(A, W)                                                                                  \
+    mstar_launch((sink_prepare_kernel<A, W>), dim3(tokens), dim3(threads), smem, s, qkv,          \
+                 (const W*)bias, (const W*)q_norm, (const W*)k_norm, freq, positions, cache_pos,  \
+                 token_req, block_table, (A*)q_out, (A*)kv_cache, a)
+    if (act_dtype == MSTAR_F32) {
+        if (weight_dtype == MSTAR_F32) { GO(float, float); } else { GO(float, bf16); }
+    } else {
+        if (weight_dtype == MSTAR_F32) { GO(bf16, float); } else { GO(bf16, bf16); }
+    }
+#undef GO
+    return launch_status();
+}
+
+// ------------------------------------------------------------------ attend (CUDA cores)
+#define SA_TILE 32
+#define SA_THREADS 128
+#define SA_MAX_ACC 32
+
+struct SinkArgs {
+    int nq, nkv, hd, vd, page_size, bt_stride, window, keep_first, q_stride;
+    float scale;
+};
+
+// The v-th key a token sees: the kept first keys come before the window's.
+__device__ __forceinline__ int visible_key(int v, int kept, int lo) { return v < kept ? v : lo + v - kept; }
+
+// One block per (token, kv head): the group's query heads share the keys and values that
+// stream through shared memory in tiles of 32 visible keys, online softmax.  Tiles are
+// anchored at the token's own first visible key, so a row's arithmetic does not depend on
+// what else is in the batch.
+template <typename A>
+__global__ void __launch_bounds__(SA_THREADS)
+sink_attention_generic_kernel(const A* __restrict__ q, A* __restrict__ out,
+                              const A* __restrict__ kv_cache, const int* __restrict__ block_table,
+                              const int* __restrict__ token_req, const int* __restrict__ cache_pos,
+                              SinkArgs a) {
+    extern __shared__ float smem[];
+    const int t = blockIdx.x, kvh = blockIdx.y;
+    const int hd = a.hd, vd = a.vd, G = a.nq / a.nkv;
+    const int wide = hd > vd ? hd : vd;
+    const int ldk = wide + 1;
+    float* qs = smem;                        // [G][hd]
+    float* tile = qs + G * hd;               // [SA_TILE][wide+1]
+    float* sc = tile + SA_TILE * ldk;        // [G][SA_TILE]
+    float* m_s = sc + G * SA_TILE;           // [G]
+    float* l_s = m_s + G;                    // [G]
+    float* alpha_s = l_s + G;                // [G]
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const unsigned long long waited = pdl_wait();
+    q = pdl_after(q, waited);
+    kv_cache = pdl_after(kv_cache, waited);
+    const int hi = cache_pos[t] + 1;
+    const int lo = (a.window > 0 && hi > a.window) ? hi - a.window : 0;
+    const int kept = a.keep_first < lo ? a.keep_first : lo;
+    const int visible = kept + hi - lo;
+    const int* bt = block_table + (size_t)token_req[t] * a.bt_stride;
+    const size_t page_elems = (size_t)a.nkv * a.page_size * (hd + vd);
+    const size_t k_head = (size_t)kvh * a.page_size * hd;
+    const size_t v_head = (size_t)a.nkv * a.page_size * hd + (size_t)kvh * a.page_size * vd;
+
+    const A* qrow = q + (size_t)t * a.q_stride + (size_t)kvh * G * hd;
+    for (int i = tid; i < G * hd; i += SA_THREADS) qs[i] = to_float(qrow[i]);
+    for (int i = tid; i < G; i += SA_THREADS) {
+        m_s[i] = -INFINITY;
+        l_s[i] = 0.f;
+    }
+    float acc[SA_MAX_ACC];
+#pragma unroll
+    for (int k = 0; k < SA_MAX_ACC; ++k) acc[k] = 0.f;
+    const int n_out = G * vd;
+    __syncthreads();
+
+    for (int base = 0; base < visible; base += SA_TILE) {
+        for (int idx = tid; idx < SA_TILE * hd; idx += SA_THREADS) {
+            const int j = idx / hd, d = idx - j * hd;
+            float v = 0.f;
+            if (base + j < visible) {
+                const int key = visible_key(base + j, kept, lo);
+                const int page = bt[key / a.page_size];
+                v = to_float(kv_cache[(size_t)page * page_elems + k_head +
+                                      (size_t)(key % a.page_size) * hd + d]);
+            }
+            tile[j * ldk + d] = v;
+        }
+        __syncthreads();
+        for (int idx = tid; idx < G * SA_TILE; idx += SA_THREADS) {
+            const int g = idx / SA_TILE, j = idx - g * SA_TILE;
+            float s = -INFINITY;
+            if (base + j < visible) {
+                const float* qv = qs + g * hd;
+                const float* kv = tile + j * ldk;
+                float dot = 0.f;
+                for (int d = 0; d < hd; ++d) dot = fmaf(qv[d], kv[d], dot);
+                s = dot * a.scale;
+            }
+            sc[idx] = s;
+        }
+        __syncthreads();
+        for (int g = warp; g < G; g += SA_THREADS / 32) {
+            const float s = sc[g * SA_TILE + lane];
+            const float m_old = m_s[g];
+            const float m_new = fmaxf(m_old, warp_max(s));  // the tile's first key is visible
+            const float p = expf(s - m_new);
+            const float psum = warp_sum(p);
+            sc[g * SA_TILE + lane] = p;
+            if (lane == 0) {
+                const float al = expf(m_old - m_new);
+                alpha_s[g] = al;
+                l_s[g] = l_s[g] * al + psum;
+                m_s[g] = m_new;
+            }
+        }
+        __syncthreads();
+        for (int idx = tid; idx < SA_TILE * vd; idx += SA_THREADS) {
+            const int j = idx / vd, d = idx - j * vd;
+            float v = 0.f;
+            if (base + j < visible) {
+                const int key = visible_key(base + j, kept, lo);
+                const int page = bt[key / a.page_size];
+                v = to_float(kv_cache[(size_t)page * page_elems + v_head +
+                                      (size_t)(key % a.page_size) * vd + d]);
+            }
+            tile[j * ldk + d] = v;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < SA_MAX_ACC; ++k) {
+            const int o = tid + k * SA_THREADS;
+            if (o < n_out) {
+                const int g = o / vd, d = o - g * vd;
+                const float* p = sc + g * SA_TILE;
+                float sum = acc[k] * alpha_s[g];
+#pragma unroll 8
+                for (int j = 0; j < SA_TILE; ++j) sum = fmaf(p[j], tile[j * ldk + d], sum);
+                acc[k] = sum;
+            }
+        }
+        __syncthreads();
+    }
+
+    A* orow = out + (size_t)t * a.nq * vd + (size_t)kvh * G * vd;
+#pragma unroll
+    for (int k = 0; k < SA_MAX_ACC; ++k) {
+        const int o = tid + k * SA_THREADS;
+        if (o < n_out) orow[o] = from_float<A>(acc[k] / l_s[o / vd]);
+    }
+}
+
+// q: [tokens] rows of q_stride elements (nq*hd used); out: [tokens, nq*vd].  Returns 0, a
+// CUDA error code, or -1 when the shape is refused.
+MSTAR_API int mstar_sink_attention_generic(const void* q, int q_stride, void* out,
+                                           const void* kv_cache, const int* block_table,
+                                           int bt_stride, const int* token_req,
+                                           const int* cache_pos, int tokens, int nq, int nkv,
+                                           int hd, int vd, int page_size, int window,
+                                           int keep_first, float scale, int act_dtype,
+                                           void* stream) {
+    if (tokens <= 0) return 0;
+    if (nkv <= 0 || nq % nkv != 0 || hd <= 0 || vd <= 0) return -1;
+    const int G = nq / nkv;
+    if (G * vd > SA_MAX_ACC * SA_THREADS) return -1;
+    const int wide = hd > vd ? hd : vd;
+    const size_t smem = sizeof(float) * ((size_t)G * hd + (size_t)SA_TILE * (wide + 1) +
+                                         (size_t)G * SA_TILE + 3 * (size_t)G);
+    if (smem > 200 * 1024) return -1;
+    cudaStream_t s = (cudaStream_t)stream;
+    SinkArgs a{nq, nkv, hd, vd, page_size, bt_stride, window, keep_first, q_stride, scale};
+    dim3 grid(tokens, nkv);
+    static size_t configured_f32 = 0, configured_bf16 = 0;
+    if (act_dtype == MSTAR_F32) {
+        if (smem > 48 * 1024 && smem > configured_f32) {
+            cudaFuncSetAttribute(sink_attention_generic_kernel<float>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            configured_f32 = smem;
+        }
+        mstar_launch((sink_attention_generic_kernel<float>), grid, dim3(SA_THREADS), smem, s,
+                     (const float*)q, (float*)out, (const float*)kv_cache, block_table, token_req,
+                     cache_pos, a);
+    } else {
+        if (smem > 48 * 1024 && smem > configured_bf16) {
+            cudaFuncSetAttribute(sink_attention_generic_kernel<bf16>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            configured_bf16 = smem;
+        }
+        mstar_launch((sink_attention_generic_kernel<bf16>), grid, dim3(SA_THREADS), smem, s,
+                     (const bf16*)q, (bf16*)out, (const bf16*)kv_cache, block_table, token_req,
+                     cache_pos, a);
+    }
+    return launch_status();
+}

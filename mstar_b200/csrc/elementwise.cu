@@ -520,16 +520,19 @@ MSTAR_API int mstar_rope_kv_write(void* qkv, int act_dtype, const int* positions
 
 // ------------------------------------------- post-norm + residual add + pre-norm
 // A sublayer whose output is normalised before it joins the residual:
-//   resid += rms(delta, post_eps) * (post_w + post_off)          (always)
-//   out    = rms(resid, eps) * (weight + w_off)                  (when out != nullptr)
+//   resid += post_scale * rms(delta, post_eps) * (post_w + post_off)   (always)
+//   out    = rms(resid, eps) * (weight + w_off)          (when out and weight are given)
+//   out    = resid in the activation type                (when out is given without a weight:
+//                                                         the next sublayer reads the residual)
 // One block per row; the row stays in shared memory between the passes.  Sums, scales and
 // the residual are float for both activation types; a row's sums are taken in an order that
 // depends only on its width.
-template <typename A, typename W>
-__global__ void add_postnorm_rmsnorm_kernel(float* __restrict__ resid, const A* __restrict__ delta,
+template <typename D, typename A, typename W>
+__global__ void add_postnorm_rmsnorm_kernel(float* __restrict__ resid, const D* __restrict__ delta,
                                             const float* __restrict__ post_w, float post_eps,
-                                            float post_off, const W* __restrict__ weight,
-                                            A* __restrict__ out, int hidden, float eps, float w_off) {
+                                            float post_off, float post_scale,
+                                            const W* __restrict__ weight, A* __restrict__ out,
+                                            int hidden, float eps, float w_off) {
     extern __shared__ float row[];
     __shared__ float scratch[32];
     const size_t base = (size_t)blockIdx.x * hidden;
@@ -543,36 +546,136 @@ __global__ void add_postnorm_rmsnorm_kernel(float* __restrict__ resid, const A* 
     const float inv_d = rsqrtf(block_sum(ss, scratch) / (float)hidden + post_eps);
     float ss2 = 0.f;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        const float h = resid[base + i] + row[i] * inv_d * (post_w[i] + post_off);
+        const float h = resid[base + i] + post_scale * (row[i] * inv_d * (post_w[i] + post_off));
         resid[base + i] = h;
         row[i] = h;
         ss2 = fmaf(h, h, ss2);
     }
     if (out == nullptr) return;
+    if (weight == nullptr) {                 // the new residual itself, in the activation type
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[base + i] = from_float<A>(row[i]);
+        return;
+    }
     const float inv = rsqrtf(block_sum(ss2, scratch) / (float)hidden + eps);
     for (int i = threadIdx.x; i < hidden; i += blockDim.x)
         out[base + i] = from_float<A>(row[i] * inv * (to_float(weight[i]) + w_off));
 }
 
-MSTAR_API int mstar_add_postnorm_rmsnorm(float* resid, const void* delta, const float* post_w,
-                                         float post_eps, float post_off, const void* weight,
-                                         int weight_dtype, void* out, int act_dtype, int rows,
-                                         int hidden, float eps, float w_off, void* stream) {
+// delta: [rows, hidden] of `delta_dtype`; out: nullptr, or [rows, hidden] of `act_dtype` (the
+// pre-normed rows when `weight` is given, the residual itself when it is not).
+MSTAR_API int mstar_add_postnorm_rmsnorm(float* resid, const void* delta, int delta_dtype,
+                                         const float* post_w, float post_eps, float post_off,
+                                         float post_scale, const void* weight, int weight_dtype,
+                                         void* out, int act_dtype, int rows, int hidden, float eps,
+                                         float w_off, void* stream) {
     if (rows <= 0) return 0;
     if (hidden <= 0 || hidden > 48 * 1024 / 4) return -1;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     const size_t smem = sizeof(float) * (size_t)hidden;
-#define LAUNCH(A, W)                                                                              \
-    mstar_launch((add_postnorm_rmsnorm_kernel<A, W>), dim3(rows), dim3(threads), smem, s, resid,  \
-                 (const A*)delta, post_w, post_eps, post_off, (const W*)weight, (A*)out, hidden,  \
-                 eps, w_off)
+#define LAUNCH(D, A, W)                                                                           \
+    mstar_launch((add_postnorm_rmsnorm_kernel<D, A, W>), dim3(rows), dim3(threads), smem, s,      \
+                 resid, (const D*)delta, post_w, post_eps, post_off, post_scale,                  \
+                 (const W*)weight, (A*)out, hidden, eps, w_off)
     if (act_dtype == MSTAR_F32) {
-        if (weight_dtype == MSTAR_F32) { LAUNCH(float, float); } else { LAUNCH(float, bf16); }
+        if (delta_dtype != MSTAR_F32) return -1;
+        if (weight_dtype == MSTAR_F32) { LAUNCH(float, float, float); } else { LAUNCH(float, float, bf16); }
+    } else if (delta_dtype == MSTAR_F32) {
+        if (weight_dtype == MSTAR_F32) { LAUNCH(float, bf16, float); } else { LAUNCH(float, bf16, bf16); }
     } else {
-        if (weight_dtype == MSTAR_F32) { LAUNCH(bf16, float); } else { LAUNCH(bf16, bf16); }
+        if (weight_dtype == MSTAR_F32) { LAUNCH(bf16, bf16, float); } else { LAUNCH(bf16, bf16, bf16); }
     }
 #undef LAUNCH
+    return launch_status();
+}
+
+// ------------------------------------------------------------ mean of normed branch outputs
+// out[r] = (1/n) sum_b rms(x_b[r]) * w_b, float out; n = 2..4 branches of the same width.
+struct BranchPtrs {
+    const void* x[4];
+    const float* w[4];
+};
+
+template <typename A>
+__global__ void mean_of_norms_kernel(BranchPtrs p, int n, float* __restrict__ out, int hidden,
+                                     float eps) {
+    __shared__ float scratch[32];
+    const size_t base = (size_t)blockIdx.x * hidden;
+    const unsigned long long waited = pdl_wait();
+    float inv[4];
+    for (int b = 0; b < n; ++b) {
+        const A* x = pdl_after((const A*)p.x[b], waited);
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            const float v = to_float(x[base + i]);
+            ss = fmaf(v, v, ss);
+        }
+        inv[b] = rsqrtf(block_sum(ss, scratch) / (float)hidden + eps);
+    }
+    const float share = 1.f / (float)n;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float sum = 0.f;
+        for (int b = 0; b < n; ++b) {
+            const A* x = pdl_after((const A*)p.x[b], waited);
+            sum += to_float(x[base + i]) * inv[b] * p.w[b][i];
+        }
+        out[base + i] = sum * share;
+    }
+}
+
+MSTAR_API int mstar_mean_of_norms(const void* x0, const void* x1, const void* x2, const void* x3,
+                                  const float* w0, const float* w1, const float* w2,
+                                  const float* w3, int n, float* out, int act_dtype, int rows,
+                                  int hidden, float eps, void* stream) {
+    if (rows <= 0) return 0;
+    if (n < 1 || n > 4 || hidden <= 0) return -1;
+    BranchPtrs p{{x0, x1, x2, x3}, {w0, w1, w2, w3}};
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (act_dtype == MSTAR_F32)
+        mstar_launch((mean_of_norms_kernel<float>), dim3(rows), dim3(threads), 0, s, p, n, out,
+                     hidden, eps);
+    else
+        mstar_launch((mean_of_norms_kernel<bf16>), dim3(rows), dim3(threads), 0, s, p, n, out,
+                     hidden, eps);
+    return launch_status();
+}
+
+// ------------------------------------------------------------ activations without a gate
+// kind 0: relu(x)^2, 1: gelu (tanh form), 2: silu.  In place or not.
+__device__ __forceinline__ float plain_activation(float v, int kind) {
+    if (kind == 0) {
+        const float r = fmaxf(v, 0.f);
+        return r * r;
+    }
+    if (kind == 1)
+        return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    return v / (1.f + expf(-v));
+}
+
+template <typename A>
+__global__ void activation_kernel(const A* __restrict__ x, A* __restrict__ out, size_t total,
+                                  int kind) {
+    x = pdl_after(x, pdl_wait());
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x)
+        out[i] = from_float<A>(plain_activation(to_float(x[i]), kind));
+}
+
+MSTAR_API int mstar_activation(const void* x, void* out, int act_dtype, long long total, int kind,
+                               void* stream) {
+    if (total <= 0) return 0;
+    if (kind < 0 || kind > 2) return -1;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = 256;
+    const long long want = (total + threads - 1) / threads;
+    const int blocks = (int)(want < 8192 ? want : 8192);
+    if (act_dtype == MSTAR_F32)
+        mstar_launch((activation_kernel<float>), dim3(blocks), dim3(threads), 0, s, (const float*)x,
+                     (float*)out, (size_t)total, kind);
+    else
+        mstar_launch((activation_kernel<bf16>), dim3(blocks), dim3(threads), 0, s, (const bf16*)x,
+                     (bf16*)out, (size_t)total, kind);
     return launch_status();
 }
 

@@ -12,7 +12,8 @@
 // the number of cached tokens (the reference's position_id_start beside seq_len,
 // kv_store.py:112-116, advanced on its own by set_custom_pos_advance,
 // cache_manager.py:777-808); pages that a window has passed are given back while
-// the request is still running; reservation of a whole batch is all-or-nothing
+// the request is still running (but for the pages of the first keys where a group keeps
+// those visible); reservation of a whole batch is all-or-nothing
 // (the reference leaves earlier requests of a failed batch extended,
 // kv_store.py:463-482); a pool of fixed-size state slots, one per live request.
 #include <cstdint>
@@ -38,6 +39,7 @@ struct Group {
     int page_size = 0;
     int num_pages = 0;
     int window = 0;  // 0: every key is kept
+    int keep_first = 0;  // with a window: keys at positions below this stay visible for ever
     std::deque<int> free_pages;
     std::vector<int64_t> owner;  // request id holding the page, or -1
 };
@@ -81,7 +83,8 @@ void release_passed(Manager& m, int64_t rid, Request& r) {
         if (g.window <= 0) continue;
         const int64_t first = first_needed_page(g, r.len);
         auto& tab = r.table[gi];
-        for (int64_t p = 0; p < first && p < (int64_t)tab.size(); ++p) {
+        // the pages that hold the kept first keys are never passed
+        for (int64_t p = ceil_div(g.keep_first, g.page_size); p < first && p < (int64_t)tab.size(); ++p) {
             if (tab[p] >= 0) {
                 g.owner[tab[p]] = -1;
                 g.free_pages.push_back(tab[p]);
@@ -94,13 +97,15 @@ void release_passed(Manager& m, int64_t rid, Request& r) {
 
 }  // namespace
 
+// keep_first: per group, or nullptr for none.
 MSTAR_API void* cm_create(int n_groups, const int* page_sizes, const int* num_pages,
-                          const int* windows, int num_slots) {
+                          const int* windows, const int* keep_first, int num_slots) {
     if (n_groups < 0 || num_slots < 0) return nullptr;
     auto* m = new Manager();
     m->groups.resize(n_groups);
     for (int i = 0; i < n_groups; ++i) {
-        if (page_sizes[i] <= 0 || num_pages[i] < 0 || windows[i] < 0) {
+        if (page_sizes[i] <= 0 || num_pages[i] < 0 || windows[i] < 0 ||
+            (keep_first != nullptr && keep_first[i] < 0)) {
             delete m;
             return nullptr;
         }
@@ -108,6 +113,7 @@ MSTAR_API void* cm_create(int n_groups, const int* page_sizes, const int* num_pa
         g.page_size = page_sizes[i];
         g.num_pages = num_pages[i];
         g.window = windows[i];
+        g.keep_first = keep_first != nullptr ? keep_first[i] : 0;
         g.owner.assign(g.num_pages, -1);
         for (int p = 0; p < g.num_pages; ++p) g.free_pages.push_back(p);
     }

@@ -4,12 +4,15 @@
 //   scores  s = sigmoid(z) or softmax(z) over a token's float router logits z
 //   chosen  the `top` largest scores (the lower index wins a tie), weight w = s, or s divided
 //           by the sum of the chosen scores when `renormalize`
+//           With a `choice_bias` the largest of s + bias are chosen; the weights stay s.
 //   expert  y = W_down (silu(W_gate u) * (W_up u)),  u = w x (`scale_input`) or u = x with
-//           w multiplying y
+//           w multiplying y; without a gate (`gated` 0) y = W_down relu(W_up u)^2
 //   out[t] = sum over the chosen experts (+ `add[t]`, the shared expert's output)
+// A chosen index at or beyond `real` (the experts that have matrices) is an identity
+// expert: it adds w x[t].
 //
 // Expert matrices are stacked expert after expert: gate_up [experts][2 * ff][width] (gate
-// rows first), down [experts][width][ff].
+// rows first; [experts][ff][width] without a gate), down [experts][width][ff].
 //
 // These are the kernels for a step's rows as they come (token by token, each row streaming
 // the weights of its experts): dot products on CUDA cores, float sums in a fixed order, so a
@@ -24,7 +27,8 @@
 // logits, so the choice is made on the logits.
 #define RT_PER_LANE 32
 
-__global__ void route_topk_kernel(const float* __restrict__ logits, int* __restrict__ chosen,
+__global__ void route_topk_kernel(const float* __restrict__ logits, const float* __restrict__ choice_bias,
+                                  int* __restrict__ chosen,
                                   float* __restrict__ weight, int tokens, int experts, int top,
                                   int softmax, int renormalize) {
     logits = pdl_after(logits, pdl_wait());
@@ -49,7 +53,10 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, int* __restr
             const int e = lane + 32 * i;
             if (e >= experts) break;
             if (!((taken >> i) & 1u)) {
-                const float v = z[e];
+                // scores are monotone in the logits; with a bias the choice needs the scores
+                float v = z[e];
+                if (choice_bias != nullptr)
+                    v = (softmax ? expf(v - zmax) / denom : 1.f / (1.f + expf(-v))) + choice_bias[e];
                 if (be == 0x7fffffff || v > bz) {
                     bz = v;
                     be = e;
@@ -66,7 +73,8 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, int* __restr
             }
         }
         if ((be & 31) == lane) taken |= 1u << (be >> 5);
-        const float s = softmax ? expf(bz - zmax) / denom : 1.f / (1.f + expf(-bz));
+        const float zb = z[be];
+        const float s = softmax ? expf(zb - zmax) / denom : 1.f / (1.f + expf(-zb));
         total += s;
         if (lane == 0) {
             chosen[(size_t)t * top + k] = be;
@@ -77,12 +85,13 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, int* __restr
         for (int k = 0; k < top; ++k) weight[(size_t)t * top + k] /= total;
 }
 
-MSTAR_API int mstar_route_topk(const float* logits, int* chosen, float* weight, int tokens,
-                               int experts, int top, int softmax, int renormalize, void* stream) {
+MSTAR_API int mstar_route_topk(const float* logits, const float* choice_bias, int* chosen,
+                               float* weight, int tokens, int experts, int top, int softmax,
+                               int renormalize, void* stream) {
     if (tokens <= 0) return 0;
     if (experts <= 0 || top <= 0 || top > experts || experts > 32 * RT_PER_LANE) return -1;
     mstar_launch(route_topk_kernel, dim3((tokens + 3) / 4), dim3(128), 0, (cudaStream_t)stream,
-                 logits, chosen, weight, tokens, experts, top, softmax, renormalize);
+                 logits, choice_bias, chosen, weight, tokens, experts, top, softmax, renormalize);
     return launch_status();
 }
 
@@ -92,11 +101,12 @@ MSTAR_API int mstar_route_topk(const float* logits, int* chosen, float* weight, 
 #define RE_THREADS 256
 #define RE_UNITS 32
 
-template <typename A>
+template <typename A, bool GATED>
 __global__ void __launch_bounds__(RE_THREADS)
 expert_gate_up_kernel(const A* __restrict__ x, const A* __restrict__ w_gate_up,
                       const int* __restrict__ chosen, const float* __restrict__ weight,
-                      float* __restrict__ act, int width, int ff, int top, int scale_input) {
+                      float* __restrict__ act, int width, int ff, int top, int scale_input,
+                      int real) {
     extern __shared__ float xs[];            // [width]
     const int row = blockIdx.x, t = row / top;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -107,8 +117,9 @@ expert_gate_up_kernel(const A* __restrict__ x, const A* __restrict__ w_gate_up,
     for (int i = threadIdx.x; i < width; i += RE_THREADS) xs[i] = to_float(x[(size_t)t * width + i]);
     __syncthreads();
     const int e = chosen[row];
+    if (e >= real) return;                     // an identity expert has no hidden units
     const float w = scale_input ? weight[row] : 1.f;
-    const A* base = w_gate_up + (size_t)e * 2 * ff * width;
+    const A* base = w_gate_up + (size_t)e * (GATED ? 2 : 1) * ff * width;
     // rows start at multiples of `width` elements: 8-element loads where that is aligned
     const bool vec = width % 8 == 0 && ((uintptr_t)w_gate_up & 31) == 0;
     // a warp takes four hidden units at a time: eight rows of weights stream side by side
@@ -122,7 +133,7 @@ expert_gate_up_kernel(const A* __restrict__ x, const A* __restrict__ w_gate_up,
                 for (int k = 0; k < 4; ++k) {
                     const int u = min(u0 + k, ff - 1);          // a unit past the end repeats the last
                     load8(base + (size_t)u * width + 8 * c, a8[k]);
-                    load8(base + (size_t)(ff + u) * width + 8 * c, b8[k]);
+                    if (GATED) load8(base + (size_t)(ff + u) * width + 8 * c, b8[k]);
                 }
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
@@ -130,7 +141,7 @@ expert_gate_up_kernel(const A* __restrict__ x, const A* __restrict__ w_gate_up,
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
                         sg[k] = fmaf(a8[k][i], xv, sg[k]);
-                        su[k] = fmaf(b8[k][i], xv, su[k]);
+                        if (GATED) su[k] = fmaf(b8[k][i], xv, su[k]);
                     }
                 }
             }
@@ -140,14 +151,22 @@ expert_gate_up_kernel(const A* __restrict__ x, const A* __restrict__ w_gate_up,
                 for (int k = 0; k < 4; ++k) {
                     const int u = min(u0 + k, ff - 1);
                     sg[k] = fmaf(to_float(base[(size_t)u * width + i]), xs[i], sg[k]);
-                    su[k] = fmaf(to_float(base[(size_t)(ff + u) * width + i]), xs[i], su[k]);
+                    if (GATED) su[k] = fmaf(to_float(base[(size_t)(ff + u) * width + i]), xs[i], su[k]);
                 }
             }
         }
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-            const float g = warp_sum(sg[k]) * w, up = warp_sum(su[k]) * w;
-            if (lane == 0 && u0 + k < u_end) act[(size_t)row * ff + u0 + k] = g / (1.f + expf(-g)) * up;
+            const float g = warp_sum(sg[k]) * w;
+            float v;
+            if (GATED) {
+                const float up = warp_sum(su[k]) * w;
+                v = g / (1.f + expf(-g)) * up;
+            } else {
+                const float r = fmaxf(g, 0.f);
+                v = r * r;
+            }
+            if (lane == 0 && u0 + k < u_end) act[(size_t)row * ff + u0 + k] = v;
         }
     }
 }
@@ -158,14 +177,16 @@ __global__ void __launch_bounds__(RE_THREADS)
 expert_down_kernel(const float* __restrict__ act, const A* __restrict__ w_down,
                    const int* __restrict__ chosen, const float* __restrict__ weight,
                    const A* __restrict__ add, A* __restrict__ out, int width, int ff, int top,
-                   int scale_input) {
+                   int scale_input, const A* __restrict__ x, int real) {
     extern __shared__ float as[];            // [top][ff]
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const unsigned long long waited = pdl_wait();
     act = pdl_after(act, waited);
     add = pdl_after(add, waited);
-    for (int i = threadIdx.x; i < top * ff; i += RE_THREADS) as[i] = act[(size_t)t * top * ff + i];
+    x = pdl_after(x, waited);
+    for (int i = threadIdx.x; i < top * ff; i += RE_THREADS)
+        as[i] = chosen[(size_t)t * top + i / ff] < real ? act[(size_t)t * top * ff + i] : 0.f;
     __syncthreads();
     const bool vec = ff % 8 == 0 && ((uintptr_t)w_down & 31) == 0;
     const int c_end = min(width, (int)(blockIdx.y + 1) * RE_UNITS);
@@ -173,6 +194,13 @@ expert_down_kernel(const float* __restrict__ act, const A* __restrict__ w_down,
         float total[4] = {0.f, 0.f, 0.f, 0.f};
         for (int k = 0; k < top; ++k) {
             const int e = chosen[(size_t)t * top + k];
+            if (e >= real) {                   // identity expert: w x[t]
+                const float wk = weight[(size_t)t * top + k];
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    total[q] += wk * to_float(x[(size_t)t * width + min(c0 + q, width - 1)]);
+                continue;
+            }
             const A* wexp = w_down + (size_t)e * width * ff;
             float s4[4] = {0.f, 0.f, 0.f, 0.f};
             if (vec) {
@@ -219,27 +247,29 @@ expert_down_kernel(const float* __restrict__ act, const A* __restrict__ w_down,
 MSTAR_API int mstar_experts_by_row(const void* x, const void* w_gate_up, const void* w_down,
                                    const int* chosen, const float* weight, float* act,
                                    const void* add, void* out, int act_dtype, int tokens,
-                                   int width, int ff, int top, int scale_input, void* stream) {
+                                   int width, int ff, int top, int scale_input, int gated,
+                                   int real, void* stream) {
     if (tokens <= 0) return 0;
     if (width <= 0 || ff <= 0 || top <= 0) return -1;
     if ((size_t)width * 4 > 48 * 1024 || (size_t)top * ff * 4 > 48 * 1024) return -1;
     cudaStream_t s = (cudaStream_t)stream;
     dim3 g1(tokens * top, (ff + RE_UNITS - 1) / RE_UNITS), g2(tokens, (width + RE_UNITS - 1) / RE_UNITS);
+#define GO(A, GATED)                                                                              \
+    mstar_launch((expert_gate_up_kernel<A, GATED>), g1, dim3(RE_THREADS), sizeof(float) * width, s, \
+                 (const A*)x, (const A*)w_gate_up, chosen, weight, act, width, ff, top,            \
+                 scale_input, real)
     if (act_dtype == MSTAR_F32) {
-        mstar_launch((expert_gate_up_kernel<float>), g1, dim3(RE_THREADS), sizeof(float) * width, s,
-                     (const float*)x, (const float*)w_gate_up, chosen, weight, act, width, ff, top,
-                     scale_input);
+        if (gated) { GO(float, true); } else { GO(float, false); }
         mstar_launch((expert_down_kernel<float>), g2, dim3(RE_THREADS), sizeof(float) * top * ff, s,
                      (const float*)act, (const float*)w_down, chosen, weight, (const float*)add,
-                     (float*)out, width, ff, top, scale_input);
+                     (float*)out, width, ff, top, scale_input, (const float*)x, real);
     } else {
-        mstar_launch((expert_gate_up_kernel<bf16>), g1, dim3(RE_THREADS), sizeof(float) * width, s,
-                     (const bf16*)x, (const bf16*)w_gate_up, chosen, weight, act, width, ff, top,
-                     scale_input);
+        if (gated) { GO(bf16, true); } else { GO(bf16, false); }
         mstar_launch((expert_down_kernel<bf16>), g2, dim3(RE_THREADS), sizeof(float) * top * ff, s,
                      (const float*)act, (const bf16*)w_down, chosen, weight, (const bf16*)add,
-                     (bf16*)out, width, ff, top, scale_input);
+                     (bf16*)out, width, ff, top, scale_input, (const bf16*)x, real);
     }
+#undef GO
     return launch_status();
 }
 
@@ -262,7 +292,8 @@ MSTAR_API int mstar_experts_by_row(const void* x, const void* w_gate_up, const v
 #define GG_LD 40          // bf16 elements between rows of a shared tile (80 bytes: no bank conflicts)
 #define GG_STAGES 3
 
-__global__ void experts_sort_kernel(const int* __restrict__ chosen, int rows, int experts, int tile_rows,
+// `experts`: all router outputs; tiles are made for the first `real` of them only.
+__global__ void experts_sort_kernel(const int* __restrict__ chosen, int rows, int experts, int real, int tile_rows,
                                     int* __restrict__ order, int* __restrict__ pos,
                                     int* __restrict__ offsets, int* __restrict__ tile_expert,
                                     int* __restrict__ tile_first, int* __restrict__ num_tiles) {
@@ -279,7 +310,7 @@ __global__ void experts_sort_kernel(const int* __restrict__ chosen, int rows, in
         for (int e = 0; e < experts; ++e) {
             offsets[e] = at;
             cursor[e] = at;
-            for (int p = at; p < at + counts[e]; p += tile_rows) {
+            for (int p = at; e < real && p < at + counts[e]; p += tile_rows) {
                 tile_expert[tiles] = e;
                 tile_first[tiles] = p;
                 ++tiles;
@@ -300,13 +331,17 @@ __global__ void experts_sort_kernel(const int* __restrict__ chosen, int rows, in
 // C tile [GG_BM x 64] of one expert's group (a warp per 32 x 32 of it).  GATED: A rows are x[order[p] / top], B rows are
 // the expert's gate rows n0.. and up rows ff + n0..; out = silu(w G) * (w U) as bfloat16.
 // Plain: A rows are act[p], B rows the expert's down rows n0..; out float.
-template <bool GATED, int GG_BM>
+// MODE 0: plain (down), 1: gated gate/up with SiLU, 2: up alone with relu^2 (A rows gathered
+// like the gated form, one block of B rows, bfloat16 out).
+template <int MODE, int GG_BM>
 __global__ void __launch_bounds__(GG_BM * 2)
 grouped_gemm_kernel(const bf16* __restrict__ a_src, const bf16* __restrict__ w, void* __restrict__ out,
                     const int* __restrict__ order, const float* __restrict__ weight,
                     const int* __restrict__ offsets, const int* __restrict__ tile_expert,
                     const int* __restrict__ tile_first, const int* __restrict__ num_tiles,
                     int N, int K, int top, int scale_input) {
+    constexpr bool GATED = MODE == 1;
+    constexpr bool GATHER = MODE != 0;
     constexpr int BROWS = GATED ? 2 * GG_BN : GG_BN;
     constexpr int GG_THREADS = GG_BM * 2;             // a warp per 32 x 32 of the tile
     extern __shared__ __align__(16) unsigned char gg_smem[];
@@ -328,7 +363,7 @@ grouped_gemm_kernel(const bf16* __restrict__ a_src, const bf16* __restrict__ w, 
 
     if (tid < GG_BM) {
         const int p = p0 + tid;
-        src_row[tid] = p < p_end ? (GATED ? order[p] / top : p) : -1;
+        src_row[tid] = p < p_end ? (GATHER ? order[p] / top : p) : -1;
     }
     __syncthreads();
     const bf16* wbase = w + (size_t)e * (GATED ? 2 : 1) * N * K;
@@ -409,7 +444,7 @@ grouped_gemm_kernel(const bf16* __restrict__ a_src, const bf16* __restrict__ w, 
             const int p = p0 + r;
             if (p >= p_end) continue;
             float wgt = 1.f;
-            if (GATED && scale_input) wgt = weight[order[p]];
+            if (GATHER && scale_input) wgt = weight[order[p]];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const int n = n0 + wn + j * 8 + 2 * t4;
@@ -421,6 +456,12 @@ grouped_gemm_kernel(const bf16* __restrict__ a_src, const bf16* __restrict__ w, 
                     bf16* o = (bf16*)out + (size_t)p * N + n;
                     o[0] = __float2bfloat16_rn(g0 / (1.f + expf(-g0)) * u0);
                     if (n + 1 < N) o[1] = __float2bfloat16_rn(g1 / (1.f + expf(-g1)) * u1);
+                } else if (MODE == 2) {
+                    const float r0 = fmaxf(acc[0][i][j][half * 2] * wgt, 0.f);
+                    const float r1 = fmaxf(acc[0][i][j][half * 2 + 1] * wgt, 0.f);
+                    bf16* o = (bf16*)out + (size_t)p * N + n;
+                    o[0] = __float2bfloat16_rn(r0 * r0);
+                    if (n + 1 < N) o[1] = __float2bfloat16_rn(r1 * r1);
                 } else {
                     float* o = (float*)out + (size_t)p * N + n;
                     o[0] = acc[0][i][j][half * 2];
@@ -434,7 +475,9 @@ grouped_gemm_kernel(const bf16* __restrict__ a_src, const bf16* __restrict__ w, 
 template <typename A>
 __global__ void experts_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos,
                                        const float* __restrict__ weight, const A* __restrict__ add,
-                                       A* __restrict__ out, int width, int top, int scale_input) {
+                                       A* __restrict__ out, int width, int top, int scale_input,
+                                       const int* __restrict__ chosen, const A* __restrict__ x,
+                                       int real) {
     const unsigned long long waited = pdl_wait();
     y = pdl_after(y, waited);
     pos = pdl_after(pos, waited);
@@ -443,6 +486,10 @@ __global__ void experts_combine_kernel(const float* __restrict__ y, const int* _
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
         float total = 0.f;
         for (int k = 0; k < top; ++k) {
+            if (chosen[(size_t)t * top + k] >= real) {     // identity expert: w x[t]
+                total += weight[(size_t)t * top + k] * to_float(x[(size_t)t * width + c]);
+                continue;
+            }
             const float v = y[(size_t)pos[(size_t)t * top + k] * width + c];
             total += scale_input ? v : v * weight[(size_t)t * top + k];
         }
@@ -457,7 +504,8 @@ __global__ void experts_combine_kernel(const float* __restrict__ y, const int* _
 MSTAR_API int mstar_experts_grouped(const void* x, const void* w_gate_up, const void* w_down,
                                     const int* chosen, const float* weight, int* ints, void* act,
                                     float* y, const void* add, void* out, int tokens, int width,
-                                    int ff, int top, int experts, int scale_input, void* stream) {
+                                    int ff, int top, int experts, int scale_input, int gated,
+                                    int real, void* stream) {
     if (tokens <= 0) return 0;
     if (width % 8 != 0 || ff % 8 != 0 || experts <= 0 || experts > 1024 || top <= 0) return -1;
     cudaStream_t s = (cudaStream_t)stream;
@@ -472,35 +520,42 @@ MSTAR_API int mstar_experts_grouped(const void* x, const void* w_gate_up, const 
     int* tile_expert = num_tiles + 1;
     int* tile_first = tile_expert + (rows / 64 + experts);
     mstar_launch(experts_sort_kernel, dim3(1), dim3(1024), sizeof(int) * 2 * experts, s, chosen, rows,
-                 experts, bm, order, pos, offsets, tile_expert, tile_first, num_tiles);
+                 experts, real, bm, order, pos, offsets, tile_expert, tile_first, num_tiles);
 #define GG_SMEM(BM, BROWS) (sizeof(bf16) * GG_STAGES * ((BM) + (BROWS)) * GG_LD + sizeof(int) * (BM))
-#define GG_GO(GATED, BM, BROWS, GRIDX, ...)                                                       \
+#define GG_GO(MODE, BM, BROWS, GRIDX, ...)                                                        \
     {                                                                                             \
         static bool configured = false;                                                           \
         const size_t bytes = GG_SMEM(BM, BROWS);                                                  \
         if (!configured && bytes > 48 * 1024) {                                                   \
-            cudaFuncSetAttribute(grouped_gemm_kernel<GATED, BM>,                                  \
+            cudaFuncSetAttribute(grouped_gemm_kernel<MODE, BM>,                                   \
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);        \
             configured = true;                                                                    \
         }                                                                                         \
-        mstar_launch((grouped_gemm_kernel<GATED, BM>), dim3(GRIDX, max_tiles), dim3((BM) * 2), bytes, s, \
+        mstar_launch((grouped_gemm_kernel<MODE, BM>), dim3(GRIDX, max_tiles), dim3((BM) * 2), bytes, s, \
                      __VA_ARGS__);                                                                \
     }
     const int gx1 = (ff + GG_BN - 1) / GG_BN, gx2 = (width + GG_BN - 1) / GG_BN;
-    if (bm == 128) {
-        GG_GO(true, 128, 2 * GG_BN, gx1, (const bf16*)x, (const bf16*)w_gate_up, act, order, weight,
+#define GG_UP(BM)                                                                                 \
+    if (gated)                                                                                    \
+        GG_GO(1, BM, 2 * GG_BN, gx1, (const bf16*)x, (const bf16*)w_gate_up, act, order, weight,  \
+              offsets, tile_expert, tile_first, num_tiles, ff, width, top, scale_input)           \
+    else                                                                                          \
+        GG_GO(2, BM, GG_BN, gx1, (const bf16*)x, (const bf16*)w_gate_up, act, order, weight,      \
               offsets, tile_expert, tile_first, num_tiles, ff, width, top, scale_input)
-        GG_GO(false, 128, GG_BN, gx2, (const bf16*)act, (const bf16*)w_down, (void*)y, order, weight,
+    if (bm == 128) {
+        GG_UP(128)
+        GG_GO(0, 128, GG_BN, gx2, (const bf16*)act, (const bf16*)w_down, (void*)y, order, weight,
               offsets, tile_expert, tile_first, num_tiles, width, ff, top, scale_input)
     } else {
-        GG_GO(true, 64, 2 * GG_BN, gx1, (const bf16*)x, (const bf16*)w_gate_up, act, order, weight,
-              offsets, tile_expert, tile_first, num_tiles, ff, width, top, scale_input)
-        GG_GO(false, 64, GG_BN, gx2, (const bf16*)act, (const bf16*)w_down, (void*)y, order, weight,
+        GG_UP(64)
+        GG_GO(0, 64, GG_BN, gx2, (const bf16*)act, (const bf16*)w_down, (void*)y, order, weight,
               offsets, tile_expert, tile_first, num_tiles, width, ff, top, scale_input)
     }
+#undef GG_UP
 #undef GG_GO
 #undef GG_SMEM
     mstar_launch((experts_combine_kernel<bf16>), dim3(tokens), dim3(256), 0, s, (const float*)y, pos,
-                 weight, (const bf16*)add, (bf16*)out, width, top, scale_input);
+                 weight, (const bf16*)add, (bf16*)out, width, top, scale_input, chosen,
+                 (const bf16*)x, real);
     return launch_status();
 }

@@ -708,28 +708,71 @@ def sample(logits: torch.Tensor, temperature, top_k=None, top_p=None, penalty=No
 # ------------------------------------------------------------------ sandwich norms
 def add_postnorm_rmsnorm(resid: torch.Tensor, delta: torch.Tensor, post_weight: torch.Tensor,
                          post_eps: float, post_offset: float, weight=None, eps: float = 0.0,
-                         weight_offset: float = 0.0, out_dtype: torch.dtype | None = None):
-    """resid += rms(delta) * (post_weight + post_offset), in place in float; with ``weight``,
-    returns rms(resid) * (weight + weight_offset) in ``out_dtype`` (else None).
-    ``post_weight`` is a float vector."""
+                         weight_offset: float = 0.0, out_dtype: torch.dtype | None = None,
+                         post_scale: float = 1.0, plain_out: bool = False):
+    """resid += post_scale * rms(delta) * (post_weight + post_offset), in place in float; with
+    ``weight``, returns rms(resid) * (weight + weight_offset) in ``out_dtype``; with
+    ``plain_out`` (and no weight), returns the new residual itself in ``out_dtype`` (the
+    residual tensor when that is float); else None.  ``post_weight`` is a float vector;
+    ``delta`` is float or of ``out_dtype``."""
     _need_cuda(resid, delta, post_weight, weight)
     assert resid.dtype == torch.float32 and resid.dim() == 2 and resid.is_contiguous()
     assert delta.shape == resid.shape and delta.is_contiguous()
     assert post_weight.dtype == torch.float32 and post_weight.numel() == resid.shape[1]
     rows, hidden = resid.shape
     out = None
+    out_dtype = out_dtype or delta.dtype
+    assert delta.dtype in (out_dtype, torch.float32)
     if weight is not None:
         assert weight.numel() == hidden and weight.is_contiguous()
-        out_dtype = out_dtype or delta.dtype
-        assert out_dtype == delta.dtype
+        out = torch.empty((rows, hidden), dtype=out_dtype, device=resid.device)
+    elif plain_out and out_dtype != torch.float32:
         out = torch.empty((rows, hidden), dtype=out_dtype, device=resid.device)
     code = lib.get("elementwise").mstar_add_postnorm_rmsnorm(
-        resid.data_ptr(), delta.data_ptr(), post_weight.data_ptr(), float(post_eps),
-        float(post_offset), _ptr(weight), _dt(weight) if weight is not None else F32, _ptr(out),
-        _dt(delta), rows, hidden, float(eps), float(weight_offset), _stream())
+        resid.data_ptr(), delta.data_ptr(), _dt(delta), post_weight.data_ptr(), float(post_eps),
+        float(post_offset), float(post_scale), _ptr(weight),
+        _dt(weight) if weight is not None else F32, _ptr(out), _DT[out_dtype], rows, hidden,
+        float(eps), float(weight_offset), _stream())
     if code == -1:
         raise KernelError(f"post-norm kernel refuses a width of {hidden}")
     check(code, "add_postnorm_rmsnorm")
+    if plain_out and weight is None and out is None:
+        return resid
+    return out
+
+
+def mean_of_norms(branches, weights, eps: float) -> torch.Tensor:
+    """float [rows, hidden]: the mean over the branches of rms(x_b) * w_b.  ``branches``: up
+    to four [rows, hidden] tensors of one dtype; ``weights``: float vectors."""
+    n = len(branches)
+    assert 1 <= n <= 4 and len(weights) == n
+    _need_cuda(*branches, *weights)
+    rows, hidden = branches[0].shape
+    for x, w in zip(branches, weights):
+        assert x.shape == (rows, hidden) and x.is_contiguous() and x.dtype == branches[0].dtype
+        assert w.dtype == torch.float32 and w.numel() == hidden
+    out = torch.empty((rows, hidden), dtype=torch.float32, device=branches[0].device)
+    xs = [b.data_ptr() for b in branches] + [0] * (4 - n)
+    ws = [w.data_ptr() for w in weights] + [0] * (4 - n)
+    check(lib.get("elementwise").mstar_mean_of_norms(
+        *xs, *ws, n, out.data_ptr(), _dt(branches[0]), rows, hidden, float(eps), _stream()),
+        "mean_of_norms")
+    return out
+
+
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def activation(x: torch.Tensor, kind: str, inplace: bool = True) -> torch.Tensor:
+    """relu(x)^2, gelu (tanh form) or silu, elementwise."""
+    _need_cuda(x)
+    assert x.is_contiguous()
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"activation {kind!r} has no kernel (known: {sorted(ACTIVATIONS)})")
+    out = x if inplace else torch.empty_like(x)
+    check(lib.get("elementwise").mstar_activation(
+        x.data_ptr(), out.data_ptr(), _dt(x), x.numel(), ACTIVATIONS[kind], _stream()),
+        "activation")
     return out
 
 
@@ -899,15 +942,19 @@ def linear_per_head(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | N
 
 
 # ------------------------------------------------------------------ routed experts
-def route_topk(logits: torch.Tensor, top: int, softmax: bool = False, renormalize: bool = False):
-    """(chosen int32 [tokens, top], weight float [tokens, top]) from float router logits."""
-    _need_cuda(logits)
+def route_topk(logits: torch.Tensor, top: int, softmax: bool = False, renormalize: bool = False,
+               choice_bias=None):
+    """(chosen int32 [tokens, top], weight float [tokens, top]) from float router logits.
+    ``choice_bias``: float [experts] added to the scores for the choice only."""
+    _need_cuda(logits, choice_bias)
     assert logits.dtype == torch.float32 and logits.dim() == 2 and logits.is_contiguous()
     tokens, experts = logits.shape
+    assert choice_bias is None or (choice_bias.dtype == torch.float32
+                                   and choice_bias.numel() == experts)
     chosen = torch.empty((tokens, top), dtype=torch.int32, device=logits.device)
     weight = torch.empty((tokens, top), dtype=torch.float32, device=logits.device)
     code = lib.get("routed_experts").mstar_route_topk(
-        logits.data_ptr(), chosen.data_ptr(), weight.data_ptr(), tokens, experts, top,
+        logits.data_ptr(), _ptr(choice_bias), chosen.data_ptr(), weight.data_ptr(), tokens, experts, top,
         int(softmax), int(renormalize), _stream())
     if code == -1:
         raise KernelError(f"cannot choose {top} of {experts} experts")
@@ -916,10 +963,15 @@ def route_topk(logits: torch.Tensor, top: int, softmax: bool = False, renormaliz
 
 
 def experts_by_row(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, chosen, weight,
-                   ff: int, scale_input: bool, add=None) -> torch.Tensor:
+                   ff: int, scale_input: bool, add=None, gated: bool = True,
+                   real: int | None = None) -> torch.Tensor:
     """sum over a token's chosen experts of down(silu(gate u) * up u) (+ ``add``), every row
     streaming its experts' matrices.  ``w_gate_up``: [experts * 2 * ff, width] (per expert
-    gate rows, then up rows), ``w_down``: [experts * width, ff]."""
+    gate rows, then up rows), ``w_down``: [experts * width, ff].  ``gated`` False: an expert
+    is down(relu(up u)^2) and ``w_gate_up`` [experts * ff, width].  ``real``: experts that
+    have matrices; a chosen index at or beyond it adds weight * x (default: all are real)."""
+    if real is None:
+        real = w_down.shape[0] // x.shape[1]
     _need_cuda(x, w_gate_up, w_down, chosen, weight, add)
     tokens, width = x.shape
     top = chosen.shape[1]
@@ -932,7 +984,7 @@ def experts_by_row(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tenso
     code = lib.get("routed_experts").mstar_experts_by_row(
         x.data_ptr(), w_gate_up.data_ptr(), w_down.data_ptr(), chosen.data_ptr(),
         weight.data_ptr(), act.data_ptr(), _ptr(add), out.data_ptr(), _dt(x), tokens, width, ff,
-        top, int(scale_input), _stream())
+        top, int(scale_input), int(gated), int(real), _stream())
     if code == -1:
         raise KernelError(f"the by-row expert kernels refuse width={width}, ff={ff}, top={top} "
                           "(a row of inputs, and of hidden units, within 48 KB)")
@@ -947,7 +999,8 @@ GROUPED_EXPERT_ROWS = 64
 
 
 def experts_grouped(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, chosen, weight,
-                    experts: int, ff: int, scale_input: bool, add=None) -> torch.Tensor:
+                    experts: int, ff: int, scale_input: bool, add=None, gated: bool = True,
+                    real: int | None = None) -> torch.Tensor:
     """The same sums as ``experts_by_row`` for many bfloat16 rows: rows sorted by expert on
     the device, each expert's rows through its matrices as 64-row tiles on the tensor cores
     (float sums), a token's choices added up in their order.  Nothing is read by the host."""
@@ -957,8 +1010,9 @@ def experts_grouped(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tens
     assert x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16
     assert w_down.dtype == torch.bfloat16 and x.is_contiguous()
     assert w_gate_up.is_contiguous() and w_down.is_contiguous()
-    assert tuple(w_gate_up.shape) == (experts * 2 * ff, width)
-    assert tuple(w_down.shape) == (experts * width, ff)
+    real = experts if real is None else real       # ``experts`` counts identity experts too
+    assert tuple(w_gate_up.shape) == (real * (2 if gated else 1) * ff, width)
+    assert tuple(w_down.shape) == (real * width, ff)
     assert add is None or (add.shape == x.shape and add.is_contiguous() and add.dtype == x.dtype)
     rows = tokens * top
     ints = torch.empty(2 * rows + experts + 2 + 2 * (rows // 64 + experts), dtype=torch.int32,
@@ -969,7 +1023,8 @@ def experts_grouped(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tens
     code = lib.get("routed_experts").mstar_experts_grouped(
         x.data_ptr(), w_gate_up.data_ptr(), w_down.data_ptr(), chosen.data_ptr(),
         weight.data_ptr(), ints.data_ptr(), act.data_ptr(), y.data_ptr(), _ptr(add),
-        out.data_ptr(), tokens, width, ff, top, experts, int(scale_input), _stream())
+        out.data_ptr(), tokens, width, ff, top, experts, int(scale_input), int(gated), int(real),
+        _stream())
     if code == -1:
         raise KernelError(f"the grouped expert kernels refuse width={width}, ff={ff}, "
                           f"experts={experts} (width and ff multiples of 8, at most 1024 experts)")
@@ -979,12 +1034,140 @@ def experts_grouped(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tens
 
 
 def routed_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, chosen, weight,
-                   experts: int, ff: int, scale_input: bool, add=None) -> torch.Tensor:
+                   experts: int, ff: int, scale_input: bool, add=None, gated: bool = True,
+                   identity: int = 0) -> torch.Tensor:
     """sum over a token's chosen experts of down(silu(gate u) * up u) (+ ``add``): sorted by
     expert on the tensor cores from ``GROUPED_EXPERT_ROWS`` bfloat16 rows on
     (MSTAR_EXPERTS=by_row: never), row by row below and in float32."""
     rows = x.shape[0] * chosen.shape[1]
     if (x.dtype == torch.bfloat16 and rows >= GROUPED_EXPERT_ROWS and x.shape[1] % 8 == 0
             and ff % 8 == 0 and experts <= 1024 and os.environ.get("MSTAR_EXPERTS") != "by_row"):
-        return experts_grouped(x, w_gate_up, w_down, chosen, weight, experts, ff, scale_input, add)
-    return experts_by_row(x, w_gate_up, w_down, chosen, weight, ff, scale_input, add)
+        return experts_grouped(x, w_gate_up, w_down, chosen, weight, experts + identity, ff,
+                               scale_input, add, gated=gated, real=experts)
+    return experts_by_row(x, w_gate_up, w_down, chosen, weight, ff, scale_input, add, gated=gated,
+                          real=experts)
+
+
+# ------------------------------------------------------------------ window attention with kept first keys
+def sink_page_elements(num_kv_heads: int, page_size: int, head_dim: int, v_dim: int) -> int:
+    """Elements of one cache page: [kv_heads, page_size, head_dim] keys, then [kv_heads,
+    page_size, v_dim] values (the two-plane layout when the sizes are equal)."""
+    return num_kv_heads * page_size * (head_dim + v_dim)
+
+
+def sink_prepare(qkv: torch.Tensor, bias, q_norm, k_norm, freq, positions, cache_pos, token_req,
+                 block_table, kv_cache: torch.Tensor, num_heads: int, num_kv_heads: int,
+                 head_dim: int, v_dim: int, rot: int, page_size: int, eps: float,
+                 out_dtype: torch.dtype) -> torch.Tensor:
+    """From the float fused projection ``qkv`` [tokens, (heads + kv_heads) * head_dim +
+    kv_heads * v_dim]: add ``bias``, norm every query and key head (``q_norm`` / ``k_norm``
+    weights of ``head_dim``, or None for no norm), rotate their first ``rot`` features
+    (``freq``: float64 [rot / 2]), write keys and values into the token's cache page, and
+    return the queries [tokens, heads * head_dim] in ``out_dtype``."""
+    _need_cuda(qkv, bias, q_norm, k_norm, freq, positions, cache_pos, token_req, block_table,
+               kv_cache)
+    assert qkv.dtype == torch.float32 and qkv.is_contiguous() and kv_cache.is_contiguous()
+    tokens = qkv.shape[0]
+    assert qkv.shape[1] == (num_heads + num_kv_heads) * head_dim + num_kv_heads * v_dim
+    assert kv_cache.dtype == out_dtype
+    assert kv_cache[0].numel() == sink_page_elements(num_kv_heads, page_size, head_dim, v_dim)
+    assert (q_norm is None) == (k_norm is None)
+    wd = F32
+    for w in (bias, q_norm, k_norm):
+        if w is not None:
+            wd = _dt(w)
+    for w in (bias, q_norm, k_norm):
+        assert w is None or (_dt(w) == wd and w.is_contiguous())
+    if rot:
+        assert freq is not None and freq.dtype == torch.float64 and freq.numel() == rot // 2
+    q = torch.empty((tokens, num_heads * head_dim), dtype=out_dtype, device=qkv.device)
+    code = lib.get("attention_sink").mstar_sink_prepare(
+        qkv.data_ptr(), _ptr(bias), _ptr(q_norm), _ptr(k_norm), wd, _ptr(freq),
+        positions.data_ptr(), cache_pos.data_ptr(), token_req.data_ptr(), block_table.data_ptr(),
+        block_table.stride(0), q.data_ptr(), kv_cache.data_ptr(), _DT[out_dtype], tokens, num_heads,
+        num_kv_heads, head_dim, v_dim, rot, page_size, float(eps), int(q_norm is not None),
+        _stream())
+    if code == -1:
+        raise KernelError(f"attention input kernel refuses head_dim={head_dim}, v_dim={v_dim}, "
+                          f"rot={rot}")
+    check(code, "sink_prepare")
+    return q
+
+
+def sink_attention(q: torch.Tensor, kv_cache: torch.Tensor, block_table, token_req, cache_pos,
+                   num_heads: int, num_kv_heads: int, head_dim: int, v_dim: int, page_size: int,
+                   window: int, keep_first: int, scale: float, ctx=None) -> torch.Tensor:
+    """Softmax attention of every token over the keys it sees: those of the last ``window``
+    positions (0: all) and the first ``keep_first`` of the sequence.  ``q``: [tokens, heads *
+    head_dim]; returns [tokens, heads * v_dim]."""
+    _need_cuda(q, kv_cache, block_table, token_req, cache_pos)
+    assert q.is_contiguous() and kv_cache.is_contiguous() and kv_cache.dtype == q.dtype
+    tokens = q.shape[0]
+    out = torch.empty((tokens, num_heads * v_dim), dtype=q.dtype, device=q.device)
+    code = lib.get("attention_sink").mstar_sink_attention_generic(
+        q.data_ptr(), q.stride(0), out.data_ptr(), kv_cache.data_ptr(), block_table.data_ptr(),
+        block_table.stride(0), token_req.data_ptr(), cache_pos.data_ptr(), tokens, num_heads,
+        num_kv_heads, head_dim, v_dim, page_size, int(window or 0), int(keep_first), float(scale),
+        _dt(q), _stream())
+    if code == -1:
+        raise KernelError(f"window attention refuses heads={num_heads}, kv_heads={num_kv_heads}, "
+                          f"head_dim={head_dim}, v_dim={v_dim}")
+    check(code, "sink_attention")
+    return out
+
+
+# ------------------------------------------------------------------ selective scan
+def selective_scan_state_size(inner: int, n_state: int, taps: int) -> int:
+    """Floats of one request's state: the convolution's last inputs [taps - 1, inner], then
+    S [inner, n_state]."""
+    return (taps - 1) * inner + inner * n_state
+
+
+def conv_silu(xz: torch.Tensor, weight, bias, token_req, qo_indptr, slots, state: torch.Tensor,
+              inner: int, taps: int) -> torch.Tensor:
+    """silu(causal convolution per channel) of the x half of ``xz`` [tokens, 2 * inner], the
+    inputs before a portion's start taken from the request's slot.  ``weight`` [inner, taps]
+    (last column: the current token), ``bias`` [inner]."""
+    _need_cuda(xz, weight, bias, token_req, qo_indptr, slots, state)
+    assert xz.dim() == 2 and xz.stride(1) == 1 and weight.is_contiguous() and bias.is_contiguous()
+    assert tuple(weight.shape) == (inner, taps) and bias.numel() == inner
+    assert weight.dtype == bias.dtype
+    assert state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1
+    tokens = xz.shape[0]
+    out = torch.empty((tokens, inner), dtype=xz.dtype, device=xz.device)
+    check(lib.get("selective_scan").mstar_conv_silu(
+        xz.data_ptr(), xz.stride(0), weight.data_ptr(), bias.data_ptr(), _dt(weight),
+        token_req.data_ptr(), qo_indptr.data_ptr(), slots.data_ptr(), state.data_ptr(),
+        state.stride(0), out.data_ptr(), _dt(xz), tokens, inner, taps, _stream()), "conv_silu")
+    return out
+
+
+def selective_scan(xc: torch.Tensor, xz: torch.Tensor, proj: torch.Tensor, w_dt, dt_bias, a_neg,
+                   d_skip, qo_indptr, slots, state: torch.Tensor, entries: int, inner: int,
+                   n_state: int, rank: int, taps: int) -> torch.Tensor:
+    """The recurrence over the tokens of ``entries`` batch entries, each continuing the state
+    in its slot (S updated in place, the convolution's window moved on by the portion).
+    ``xc`` [tokens, inner] conv outputs; ``xz`` [tokens, 2 * inner] (the gate z is its second
+    half, the raw x its first); ``proj`` float [tokens, rank + 2 * n_state] = [dt_in | B | C];
+    float ``w_dt`` [inner, rank], ``dt_bias`` [inner], ``a_neg`` [inner, n_state] (= -exp(A_log)),
+    ``d_skip`` [inner].  Returns y * silu(z) [tokens, inner] in the dtype of ``xc``."""
+    _need_cuda(xc, xz, proj, w_dt, dt_bias, a_neg, d_skip, qo_indptr, slots, state)
+    assert xc.is_contiguous() and xz.stride(1) == 1 and xz.dtype == xc.dtype
+    assert proj.dtype == torch.float32 and proj.is_contiguous()
+    assert proj.shape[1] == rank + 2 * n_state
+    for t, shape in ((w_dt, (inner, rank)), (dt_bias, (inner,)), (a_neg, (inner, n_state)),
+                     (d_skip, (inner,))):
+        assert t.dtype == torch.float32 and t.is_contiguous() and tuple(t.shape) == shape
+    assert state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1
+    assert state.shape[1] == selective_scan_state_size(inner, n_state, taps)
+    out = torch.empty_like(xc)
+    code = lib.get("selective_scan").mstar_selective_scan(
+        xc.data_ptr(), xz.data_ptr(), xz.stride(0), proj.data_ptr(), w_dt.data_ptr(),
+        dt_bias.data_ptr(), a_neg.data_ptr(), d_skip.data_ptr(), qo_indptr.data_ptr(),
+        slots.data_ptr(), state.data_ptr(), state.stride(0), out.data_ptr(), _dt(xc), entries,
+        inner, n_state, rank, taps, _stream())
+    if code == -1:
+        raise KernelError(f"selective scan refuses inner={inner}, state={n_state}, rank={rank} "
+                          "(at most 256 states a channel)")
+    check(code, "selective_scan")
+    return out

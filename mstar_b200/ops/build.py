@@ -44,6 +44,8 @@ LIBRARIES = {
     "matrix_memory": ("cuda", ["matrix_memory.cu"], []),
     "attention_latent": ("cuda", ["attention_latent.cu"], []),
     "routed_experts": ("cuda", ["routed_experts.cu"], []),
+    "attention_sink": ("cuda", ["attention_sink.cu"], []),
+    "selective_scan": ("cuda", ["selective_scan.cu"], []),
     "host": ("host", ["host/cache_manager.cpp"], []),
 }
 

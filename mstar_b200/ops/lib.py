@@ -27,8 +27,11 @@ _SIGNATURES = {
         "mstar_convert": [_vp, _i, _vp, _i, _ll, _vp],
         "mstar_rope_kv_write": [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i,
                                 _i, _i, _vp],
-        "mstar_add_postnorm_rmsnorm": [_vp, _vp, _vp, _f, _f, _vp, _i, _vp, _i, _i, _i, _f, _f,
-                                       _vp],
+        "mstar_add_postnorm_rmsnorm": [_vp, _vp, _i, _vp, _f, _f, _f, _vp, _i, _vp, _i, _i, _i, _f,
+                                       _f, _vp],
+        "mstar_mean_of_norms": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _f,
+                                _vp],
+        "mstar_activation": [_vp, _vp, _i, _ll, _i, _vp],
         "mstar_sigmoid_gate_mul": [_vp, _vp, _i, _i, _i, _i, _vp],
     },
     "matrix_memory": {
@@ -43,11 +46,23 @@ _SIGNATURES = {
                               _i, _i, _i, _i, _f, _vp],
     },
     "routed_experts": {
-        "mstar_route_topk": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+        "mstar_route_topk": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
         "mstar_experts_by_row": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
-                                 _vp],
+                                 _i, _i, _vp],
         "mstar_experts_grouped": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
-                                  _i, _i, _vp],
+                                  _i, _i, _i, _i, _vp],
+    },
+    "attention_sink": {
+        "mstar_sink_prepare": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i,
+                               _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
+        "mstar_sink_attention_generic": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i,
+                                         _i, _i, _i, _f, _i, _vp],
+    },
+    "selective_scan": {
+        "mstar_conv_silu": [_vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i,
+                            _vp],
+        "mstar_selective_scan": [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _vp,
+                                 _i, _i, _i, _i, _i, _i, _vp],
     },
     "attention_generic": {
         "mstar_paged_attention_generic": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i,

@@ -9,8 +9,16 @@ to the end of the key sequence, optionally limited to a window of keys.
 
 A layer with ``shares_kv`` has only the query and output products and reads the
 cache that an earlier layer wrote.
+
+Beyond that plain form a spec may ask for biases on q, k and v, an RMS norm per query and
+key head before the position encoding, a value size other than the key size, and a window
+that keeps the sequence's first keys visible (``keep_first``).  Such a layer takes the fused
+product in float, a kernel that adds the bias, norms, rotates and fills the cache pages, and
+an attention kernel that walks the kept first keys and the window's keys.
 """
 from __future__ import annotations
+
+import torch
 
 from .. import ops
 from ..weights.names import ParamSpec
@@ -27,29 +35,53 @@ class Attention:
     @classmethod
     def param_specs(cls, spec) -> dict:
         q_rows = spec.num_heads * spec.head_dim
-        kv_rows = spec.num_kv_heads * spec.head_dim
+        kv_rows = spec.num_kv_heads * (spec.head_dim + spec.value_dim)
         if spec.shares_kv:
             first = {"q.weight": ParamSpec((q_rows, spec.hidden_size))}
         else:
-            first = {"qkv.weight": ParamSpec((q_rows + 2 * kv_rows, spec.hidden_size))}
-        first["o.weight"] = ParamSpec((spec.hidden_size, q_rows))
+            first = {"qkv.weight": ParamSpec((q_rows + kv_rows, spec.hidden_size))}
+            if spec.bias:
+                first["qkv.bias"] = ParamSpec((q_rows + kv_rows,), role="vector", init="zeros")
+        if spec.qk_norm_eps is not None:
+            first["q_norm.weight"] = ParamSpec((spec.head_dim,), role="vector", init="ones")
+            first["k_norm.weight"] = ParamSpec((spec.head_dim,), role="vector", init="ones")
+        first["o.weight"] = ParamSpec((spec.hidden_size, spec.num_heads * spec.value_dim))
         return first
 
     @classmethod
     def cache_need(cls, spec) -> CacheNeed:
         return CacheNeed(kv=KVNeed(num_kv_heads=spec.num_kv_heads, head_dim=spec.head_dim,
-                                   window=spec.window))
+                                   window=spec.window, keep_first=spec.keep_first if spec.window
+                                   else 0,
+                                   v_head_dim=None if spec.value_dim == spec.head_dim
+                                   else spec.value_dim))
 
     def __init__(self, spec, params: dict, runtime: Runtime):
         if spec.num_heads % spec.num_kv_heads:
             raise ValueError(f"num_heads {spec.num_heads} is not a multiple of num_kv_heads "
                              f"{spec.num_kv_heads}")
-        if spec.head_dim % 16:
+        if spec.plain and spec.head_dim % 16:
             raise ValueError(f"head_dim {spec.head_dim} must be a multiple of 16")
+        if not spec.plain and spec.shares_kv:
+            raise ValueError("a layer that reads another layer's keys takes the plain attention")
         self.spec = spec
         self.runtime = runtime
         self.w_in = params["q.weight"] if spec.shares_kv else params["qkv.weight"]
         self.w_out = params["o.weight"]
+        self.bias = params.get("qkv.bias")
+        self.q_norm, self.k_norm = params.get("q_norm.weight"), params.get("k_norm.weight")
+        if not spec.plain:
+            from .rope import rope_inverse_frequencies
+
+            p = spec.position
+            if p.kind not in ("rope", "none") or p.interleaved:
+                raise ValueError("this attention rotates split-half pairs (a rope position spec "
+                                 "without interleaving) or nothing")
+            self.rot = p.rotary_dim if p.kind == "rope" else 0
+            self.freq = None
+            if self.rot:
+                self.freq = torch.tensor(rope_inverse_frequencies(p), dtype=torch.float64,
+                                         device=runtime.device)
         self.position = build_part("position", spec.position, {}, runtime)
         # a position part may offer the first product and its own work as one call
         self._fused_projection = getattr(self.position, "project_and_apply", None)
@@ -57,6 +89,8 @@ class Attention:
 
     def forward(self, x, ctx: StepContext, cache: LayerCache):
         s = self.spec
+        if not s.plain:
+            return self._forward_general(x, ctx, cache)
         write_heads = 0 if s.shares_kv else s.num_kv_heads
         qkv = None
         if self._fused_projection is not None and not s.shares_kv:
@@ -69,6 +103,19 @@ class Attention:
                                 cache.page_size, s.num_heads, write_heads)
         out = qkv.new_empty((ctx.num_tokens, s.num_heads * s.head_dim))
         self.attend(qkv, out, ctx, cache)
+        return ops.linear(out, self.w_out, static_weights=True)
+
+    def _forward_general(self, x, ctx: StepContext, cache: LayerCache):
+        s = self.spec
+        qkv = ops.linear(x, self.w_in, out_dtype=torch.float32, static_weights=True)
+        q = ops.sink_prepare(qkv, self.bias, self.q_norm, self.k_norm, self.freq, ctx.positions,
+                             ctx.cache_pos, ctx.token_req, cache.block_table, cache.kv,
+                             s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim, self.rot,
+                             cache.page_size, s.qk_norm_eps or 0.0, self.runtime.dtype)
+        out = ops.sink_attention(q, cache.kv, cache.block_table, ctx.token_req, ctx.cache_pos,
+                                 s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim,
+                                 cache.page_size, s.window or 0, s.keep_first if s.window else 0,
+                                 self.scale, ctx=ctx)
         return ops.linear(out, self.w_out, static_weights=True)
 
     def attend(self, qkv, out, ctx: StepContext, cache: LayerCache) -> None:

@@ -11,13 +11,18 @@ import torch
 @dataclass(frozen=True)
 class KVNeed:
     """Keys and values in pages: [pages, planes, num_kv_heads, page_size, head_dim].
-    ``window`` None keeps every key; W keeps the last W.  ``planes``: 2 for keys and values,
-    1 for a mixer that keeps one row per token (a latent that both are made from)."""
+    ``window`` None keeps every key; W keeps the last W, and the first ``keep_first`` beside
+    them.  ``planes``: 2 for keys and values, 1 for a mixer that keeps one row per token (a
+    latent that both are made from).  ``v_head_dim``: not None and other than ``head_dim``
+    makes a page [num_kv_heads, page_size, head_dim] keys followed by [num_kv_heads,
+    page_size, v_head_dim] values, and the cache tensor [pages, elements of a page]."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     planes: int = 2
+    keep_first: int = 0
+    v_head_dim: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -121,5 +126,20 @@ class ResidualStream:
     def settle(self) -> None:
         """Add a pending delta that carries its own norm into ``h`` now."""
         if self.delta is not None and self.post is not None:
+            scale = self.post_scale
             d, post = self.take_pending()
-            post.add_normed(self.h, d)
+            post.add_normed(self.h, d, scale)
+
+    def rows(self, dtype: torch.dtype) -> torch.Tensor:
+        """The residual itself, everything pending added, as rows of ``dtype`` for a sublayer
+        that reads it without a norm (the float residual tensor when ``dtype`` is float)."""
+        from .. import ops
+
+        if self.delta is not None and self.post is not None:
+            scale = self.post_scale
+            d, post = self.take_pending()
+            return post.add_normed(self.h, d, scale, rows_dtype=dtype)
+        if self.delta is not None:
+            d = self.take_delta()
+            self.h.add_(d.float() if d.dtype != torch.float32 else d)
+        return ops.convert(self.h, dtype)

@@ -95,5 +95,52 @@ class SandwichBlock:
             stream.push(self.ffn.forward(y, ctx), post=self.norm2_post)
 
 
+class PostNormBlock:
+    """h += m * norm1_post(mixer(h)); h += m * norm2_post(ffn(h)): the sublayers read the
+    residual itself, only their outputs are normed (and multiplied by ``residual_mult``).  A
+    sublayer's output stays pending with its norm; the kernel that adds it also hands the new
+    residual, in the compute dtype, to the sublayer that reads it next."""
+
+    @staticmethod
+    def _subparts(spec):
+        parts = [("mixer", "mixer"), ("norm1_post", "norm")]
+        if spec.ffn is not None:
+            parts += [("ffn", "ffn"), ("norm2_post", "norm")]
+        return parts
+
+    @classmethod
+    def param_specs(cls, spec) -> dict:
+        out = {}
+        for name, category in cls._subparts(spec):
+            sub = getattr(spec, name)
+            if sub is None:
+                raise ValueError(f"a postnorm block needs {name}")
+            for local, ps in part_class(category, sub).param_specs(sub).items():
+                out[f"{name}.{local}"] = ps
+        return out
+
+    @classmethod
+    def cache_need(cls, spec):
+        return part_class("mixer", spec.mixer).cache_need(spec.mixer)
+
+    def __init__(self, spec, params: dict, runtime: Runtime):
+        self.spec = spec
+        self.runtime = runtime
+        self.parts = {name: build_part(category, getattr(spec, name), _sub(params, name), runtime)
+                      for name, category in self._subparts(spec)}
+        self.mixer, self.norm1_post = self.parts["mixer"], self.parts["norm1_post"]
+        self.ffn, self.norm2_post = self.parts.get("ffn"), self.parts.get("norm2_post")
+        self.graph_safe = all(getattr(p, "graph_safe", False) is True for p in self.parts.values())
+
+    def forward(self, stream: ResidualStream, ctx, cache) -> None:
+        m = self.spec.residual_mult
+        x = stream.rows(self.runtime.dtype)
+        stream.push(self.mixer.forward(x, ctx, cache), post=self.norm1_post, scale=m)
+        if self.ffn is not None:
+            y = stream.rows(self.runtime.dtype)
+            stream.push(self.ffn.forward(y, ctx), post=self.norm2_post, scale=m)
+
+
 register_part("block", "prenorm", PreNormBlock)
+register_part("block", "postnorm", PostNormBlock)
 register_part("block", "sandwich", SandwichBlock)

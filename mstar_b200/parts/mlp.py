@@ -31,4 +31,32 @@ class GatedMLP:
                           static_weights=True)
 
 
+class MLP:
+    """down(act(up(x))) without a gate; the activation (relu squared, tanh gelu or silu) is
+    a kernel of its own between the two products."""
+
+    graph_safe = True
+
+    @classmethod
+    def param_specs(cls, spec) -> dict:
+        return {
+            "up.weight": ParamSpec((spec.intermediate_size, spec.hidden_size)),
+            "down.weight": ParamSpec((spec.hidden_size, spec.intermediate_size)),
+        }
+
+    def __init__(self, spec, params: dict, runtime: Runtime):
+        if spec.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"mlp activation {spec.activation!r} has no kernel "
+                             f"({sorted(ops.ACTIVATIONS)} have)")
+        self.spec = spec
+        self.runtime = runtime
+        self.up = params["up.weight"]
+        self.down = params["down.weight"]
+
+    def forward(self, x, ctx):
+        h = ops.activation(ops.linear(x, self.up, static_weights=True), self.spec.activation)
+        return ops.linear(h, self.down, static_weights=True)
+
+
 register_part("ffn", "gated_mlp", GatedMLP)
+register_part("ffn", "mlp", MLP)

@@ -39,22 +39,27 @@ class RMSNorm:
             self._weight_f32 = self.weight.float().contiguous()
         return self._weight_f32
 
-    def add_normed(self, resid: torch.Tensor, delta: torch.Tensor) -> None:
-        """resid += norm(delta): this norm applied to a part's output on its way into the
-        float residual (the norm after a sublayer)."""
-        ops.add_postnorm_rmsnorm(resid, delta, self._float_weight(), self.spec.eps,
-                                 self.spec.weight_offset)
+    def add_normed(self, resid: torch.Tensor, delta: torch.Tensor, scale: float = 1.0,
+                   rows_dtype=None):
+        """resid += scale * norm(delta): this norm applied to a part's output on its way into
+        the float residual (the norm after a sublayer).  With ``rows_dtype`` the new residual
+        is returned as rows of that dtype, from the same kernel."""
+        return ops.add_postnorm_rmsnorm(resid, delta, self._float_weight(), self.spec.eps,
+                                        self.spec.weight_offset, post_scale=scale,
+                                        out_dtype=rows_dtype, plain_out=rows_dtype is not None)
 
     def add_norm(self, stream: ResidualStream) -> torch.Tensor:
         """Fold the pending delta into the residual and return the normed rows."""
+        scale = stream.post_scale
         delta, post = stream.take_pending()
         if post is not None:
             if isinstance(post, RMSNorm):
                 # the sublayer's own norm, the residual sum and this norm as one kernel
                 return ops.add_postnorm_rmsnorm(
                     stream.h, delta, post._float_weight(), post.spec.eps, post.spec.weight_offset,
-                    self.weight, self.spec.eps, self.spec.weight_offset, self.runtime.dtype)
-            post.add_normed(stream.h, delta)
+                    self.weight, self.spec.eps, self.spec.weight_offset, self.runtime.dtype,
+                    post_scale=scale)
+            post.add_normed(stream.h, delta, scale)
             delta = None
         # a pending delta is the output of the part before: its kernels lie between this
         # norm and whatever wrote the residual last

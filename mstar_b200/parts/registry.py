@@ -71,4 +71,4 @@ def _builtin() -> None:
         return
     _done = True
     from . import (attention, block, embedding, latent_attention, matrix_memory, mlp, norm,  # noqa: F401
-                   rope, routed_experts)   # (they register themselves)
+                   parallel, rope, routed_experts, selective_scan)   # (they register themselves)
