@@ -60,7 +60,7 @@ class VudivikConfig(ModelConfig):
         cfg = cls(width=width, vocab=vocab, norm_eps=eps, residual_mult=mult,
                   layers=copy.deepcopy(list(layers)), stop_tokens=tuple(int(t) for t in stops))
         rd.positive("config", width=width, vocab=vocab, **{"norm.eps": eps})
-        if not rd.problems:
+        if width > 0:
             cfg._plan(rd)
         if rd.problems:
             raise ConfigError("unusable Vudivik configuration: " + "; ".join(rd.problems))

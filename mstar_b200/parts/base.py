@@ -95,19 +95,23 @@ class ResidualStream:
     part.  Norm parts fold ``h += delta`` into the normalisation that follows, so
     the residual sum is a 32-bit sum and costs no pass of its own.  A delta may be pushed
     with a norm of its own (``post``: a norm part), which is applied to it on its way into
-    the residual: ``h += post(delta)``."""
+    the residual, together with a multiplier: ``h += scale * post(delta)``."""
 
     def __init__(self, h: torch.Tensor):
         assert h.dtype == torch.float32
         self.h = h
         self.delta: Optional[torch.Tensor] = None
         self.post = None
+        self.post_scale = 1.0
 
-    def push(self, delta: torch.Tensor, post=None) -> None:
+    def push(self, delta: torch.Tensor, post=None, scale: float = 1.0) -> None:
         if self.delta is not None:
             raise RuntimeError("a part's output was pushed before the previous one was added")
+        if post is None and scale != 1.0:
+            raise ValueError("a multiplier goes with a norm on the part's output")
         self.delta = delta
         self.post = post
+        self.post_scale = float(scale)
 
     def take_delta(self) -> Optional[torch.Tensor]:
         """The pending delta as it is to be added.  One that carries a norm of its own is
