@@ -5,7 +5,7 @@ one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--rounds R] [--page-size P]
                     [--impl ours|reference] [--workloads all|none|mixed64|long8]
-    python bench.py --arch tifosun [--arch-size small|medium]     (another architecture)
+    python bench.py --arch tifosun|vudivik [--arch-size small|medium]   (another architecture)
 
 One JSON line on stdout.  ``value``: decoded tokens per second of the engine's step
 function plus greedy sampling, timed on the device with CUDA events: W warm-up steps, then
@@ -373,22 +373,15 @@ def tifosun_sizes(name: str) -> tuple:
     return tifosun, llama
 
 
-def arch_bench(args) -> int:
-    """``--arch tifosun``: prefill and decode throughput of the Tifosun decoder (random
-    weights, bfloat16) at ``--arch-size``, beside the Llama decoder at equal size, through the
-    same step function; and its own kernels alone at those sizes with what each has to move
-    or compute, against the measured peaks.  One JSON line."""
+def _time_models(args, models, out: dict) -> None:
+    """Prefill of one prompt and a decode step at ``args.batch`` for each (name, raw config),
+    through the step function, into ``out["models"]``."""
     import torch
 
-    from mstar_b200 import ops
-    from mstar_b200.engine.step import make_stepper
+    from mstar_b200.engine.step import StepEntry, make_stepper
 
-    pk = peaks()
-    t_cfg, l_cfg = tifosun_sizes(args.arch_size)
     page, batch = args.page_size, args.batch
-    out = {"arch": "Tifosun", "size": args.arch_size, "batch": batch, "prompt_len": PROMPT_LEN,
-           "peaks": pk["source"], "models": {}, "kernels": {}}
-    for name, raw in (("tifosun", t_cfg), ("llama", l_cfg)):
+    for name, raw in models:
         print(f"[bench] {name} at the {args.arch_size} sizes ...", file=sys.stderr, flush=True)
         model = build_model(raw)
         cfg = {"vocab_size": model.vocab_size}
@@ -397,7 +390,6 @@ def arch_bench(args) -> int:
         toks = prompts(7, model.vocab_size, PROMPT_LEN, seed=99)
         times = []
         for i, t in enumerate(toks):
-            from mstar_b200.engine.step import StepEntry
             stepper.add_request(f"p{i}")
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
@@ -417,6 +409,25 @@ def arch_bench(args) -> int:
             "decode_tok_s": round(dec["tokens_per_s"], 1), "launches_per_step": dec["launches"] // args.steps}
         del stepper, model
         torch.cuda.empty_cache()
+
+
+def arch_bench(args) -> int:
+    """``--arch tifosun``: prefill and decode throughput of the Tifosun decoder (random
+    weights, bfloat16) at ``--arch-size``, beside the Llama decoder at equal size, through the
+    same step function; and its own kernels alone at those sizes with what each has to move
+    or compute, against the measured peaks.  One JSON line."""
+    import torch
+
+    from mstar_b200 import ops
+
+    if args.arch == "vudivik":
+        return vudivik_bench(args)
+    pk = peaks()
+    t_cfg, l_cfg = tifosun_sizes(args.arch_size)
+    page, batch = args.page_size, args.batch
+    out = {"arch": "Tifosun", "size": args.arch_size, "batch": batch, "prompt_len": PROMPT_LEN,
+           "peaks": pk["source"], "models": {}, "kernels": {}}
+    _time_models(args, (("tifosun", t_cfg), ("llama", l_cfg)), out)
 
     # ---- the new kernels alone, at the sizes of one layer
     dev = "cuda:0"
@@ -518,6 +529,202 @@ def arch_bench(args) -> int:
         nbytes = tokens * width * (4 + 4 + 2 + 2.0)
         K[f"postnorm_add_norm_{label}"] = {"ms": round(ms, 4), "gbs": round(nbytes / ms / 1e6, 1),
                                            "frac_hbm": round(nbytes / ms / 1e6 / pk["hbm_gbs"], 4)}
+    ops.check_error_word(dev)
+    print(json.dumps(out))
+    return 0
+
+
+# ------------------------------------------------------------------ a third architecture
+def vudivik_sizes(name: str) -> tuple:
+    """(Vudivik config, Llama config of equal size) at layer sizes that resemble a real
+    model's: every layer a windowed attention with four kept first keys beside a selective
+    scan, feed-forwards dense and routed in turn.  The Llama beside it has the same width,
+    depth, vocabulary, heads and key/value heads, and a gated feed-forward with as many
+    weights as the dense relu-squared one."""
+    if name == "small":
+        width, depth, vocab = 1024, 8, 32000
+        left = dict(heads=8, kv_heads=2, dim=128, vdim=128, scale=128 ** -0.5)
+        right = dict(inner=2048, state=16, dt_rank=64, conv=4)
+        window, dense, experts, top, ff = 1024, 4096, 16, 2, 1024
+    elif name == "medium":
+        width, depth, vocab = 2048, 12, 64000
+        left = dict(heads=16, kv_heads=4, dim=128, vdim=128, scale=128 ** -0.5)
+        right = dict(inner=4096, state=16, dt_rank=128, conv=4)
+        window, dense, experts, top, ff = 1024, 8192, 32, 4, 1024
+    else:
+        raise ValueError(f"unknown size {name!r} (small, medium)")
+    left.update(mask={"size": window, "keep_first": 4},
+                rot={"base": 1000000.0, "dims": 128,
+                     "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}})
+    moe = {"kind": "moe", "router": {"experts": experts, "identity": 2, "top": top},
+           "expert": {"ff": ff}}
+    layers = [{"type": "parallel", "mixer": {"left": dict(left), "right": dict(right)},
+               "mlp": moe if i % 2 else {"kind": "dense", "ff": dense}} for i in range(depth)]
+    vudivik = {"architecture": "Vudivik", "width": width, "vocab": vocab, "norm": {"eps": 1e-6},
+               "residual_mult": 0.5, "layers": layers}
+    llama = dict(ORPHEUS_3B, num_hidden_layers=depth, hidden_size=width,
+                 num_attention_heads=left["heads"], num_key_value_heads=left["kv_heads"],
+                 head_dim=128, intermediate_size=dense * 2 // 3 // 256 * 256, vocab_size=vocab,
+                 tie_word_embeddings=False)
+    return vudivik, llama
+
+
+def vudivik_bench(args) -> int:
+    """``--arch vudivik``: prefill and decode throughput of the Vudivik decoder (random
+    weights, bfloat16) beside the Llama decoder at equal size, through the same step
+    function; then its own kernels alone at the sizes of one layer, each beside the like
+    kernel of the Llama (attention) or Tifosun (recurrence, experts) decoder where there is
+    one, with what each has to move or compute against the measured peaks.  One JSON line."""
+    import torch
+
+    from mstar_b200 import ops
+    from mstar_b200.parts.base import StepContext
+
+    pk = peaks()
+    v_cfg, l_cfg = vudivik_sizes(args.arch_size)
+    page, batch = args.page_size, args.batch
+    out = {"arch": "Vudivik", "size": args.arch_size, "batch": batch, "prompt_len": PROMPT_LEN,
+           "peaks": pk["source"], "models": {}, "kernels": {}}
+    _time_models(args, (("vudivik", v_cfg), ("llama", l_cfg)), out)
+
+    dev = "cuda:0"
+    g = torch.Generator(device=dev).manual_seed(0)
+
+    def rnd(*shape, scale=1.0):
+        return (scale * torch.randn(*shape, generator=g, device=dev)).to(torch.bfloat16)
+
+    def i32(v):
+        return torch.tensor(v, dtype=torch.int32, device=dev)
+
+    def record(name, ms, nbytes=None, flops=None, **more):
+        row = {"ms": round(ms, 4)}
+        if nbytes is not None:
+            row["gbs"] = round(nbytes / ms / 1e6, 1)
+            row["frac_hbm"] = round(nbytes / ms / 1e6 / pk["hbm_gbs"], 4)
+        if flops is not None:
+            row["tflops"] = round(flops / ms / 1e9, 2)
+            row["frac_bf16"] = round(flops / ms / 1e9 / pk["bf16_tflops"], 5)
+        row.update(more)
+        out["kernels"][name] = row
+
+    width = v_cfg["width"]
+    left, right = v_cfg["layers"][0]["mixer"]["left"], v_cfg["layers"][0]["mixer"]["right"]
+    moe = v_cfg["layers"][1]["mlp"]
+    H, G, hd = left["heads"], left["kv_heads"], left["dim"]
+    window, keep = left["mask"]["size"], left["mask"]["keep_first"]
+    ctx_len = PROMPT_LEN
+    pages_per = -(-ctx_len // page)
+    for tokens, reqs, label in ((batch, batch, "decode"), (PROMPT_LEN, 1, "prefill")):
+        per = tokens // reqs
+        seen = min(ctx_len, window + keep + per)
+        copies = 1 if label == "prefill" else max(1, -(-(160 << 20) // (reqs * seen * G * hd * 4)))
+        caches = [rnd(reqs * pages_per + 1, 2, G, page, hd) for _ in range(copies)]
+        table = torch.randperm(reqs * pages_per, device=dev).to(torch.int32).view(reqs, pages_per)
+        token_req = i32([r for r in range(reqs) for _ in range(per)])
+        cache_pos = i32([ctx_len - per + k for _ in range(reqs) for k in range(per)])
+        indptr = i32([k * per for k in range(reqs + 1)])
+        kv_len = i32([ctx_len] * reqs)
+        q = rnd(tokens, H * hd)
+        sc = StepContext(num_tokens=tokens, num_entries=reqs, token_req=token_req,
+                         positions=cache_pos, cache_pos=cache_pos, qo_indptr=indptr, kv_len=kv_len,
+                         slots=i32(list(range(reqs))), q_lens=[per] * reqs, kv_lens=[ctx_len] * reqs,
+                         host_slots=list(range(reqs)), max_q_len=per, max_kv_len=ctx_len,
+                         num_decode=reqs if per == 1 else 0)
+        turn = {"i": 0}
+
+        def attend():
+            c = caches[turn["i"] % copies].view(reqs * pages_per + 1, -1)
+            turn["i"] += 1
+            return ops.sink_attention(q, c, table, token_req, cache_pos, H, G, hd, hd, page, window,
+                                      keep, left["scale"], ctx=sc)
+
+        reps = max(copies, 4) if label == "decode" else 2
+        ms = _time_graph(attend, reps=reps)
+        keys = sum(min(ctx_len - per + k + 1, window + keep) for k in range(per)) * reqs
+        record(f"window_attention_{label}", ms, nbytes=reqs * seen * G * hd * 4.0,
+               flops=4.0 * H * keys * hd)
+        # the Llama decoder's attention on the same cache: every key (no window)
+        out_l = torch.empty(tokens, H * hd, dtype=torch.bfloat16, device=dev)
+        turn["i"] = 0
+        if label == "decode":
+            def llama_attend():
+                c = caches[turn["i"] % copies]
+                turn["i"] += 1
+                ops.paged_decode_attention(q, q.stride(0), out_l, c, table, token_req, cache_pos,
+                                           tokens, H, G, hd, page, 0, left["scale"], ctx_len)
+            all_keys, all_bytes = reqs * ctx_len, reqs * ctx_len * G * hd * 4.0
+        else:
+            def llama_attend():
+                ops.paged_prefill_attention(q, q.stride(0), out_l, caches[0], table, indptr, kv_len,
+                                            0, reqs, per, H, G, hd, page, 0, left["scale"])
+            all_keys, all_bytes = per * (per + 1) // 2, ctx_len * G * hd * 4.0
+        ms = _time_graph(llama_attend, reps=reps)
+        record(f"llama_attention_{label}", ms, nbytes=all_bytes, flops=4.0 * H * all_keys * hd)
+
+    inner, N, R, taps = right["inner"], right["state"], right["dt_rank"], right["conv"]
+    size = ops.selective_scan_state_size(inner, N, taps)
+    copies = max(1, -(-(160 << 20) // (size * 4 * batch)))
+    state = torch.zeros(copies * batch + 1, size, device=dev)
+    w_dt = torch.randn(inner, R, device=dev) * R ** -0.5
+    dt_bias = torch.full((inner,), -3.0, device=dev)
+    a_neg = -torch.rand(inner, N, device=dev) * 4 - 0.5
+    d_skip = torch.ones(inner, device=dev)
+    conv_w, conv_b = rnd(inner, taps), rnd(inner)
+    for tokens, entries, label in ((batch, batch, "decode"), (PROMPT_LEN, 1, "prefill")):
+        per = tokens // entries
+        xz, xc = rnd(tokens, 2 * inner), rnd(tokens, inner)
+        proj = torch.randn(tokens, R + 2 * N, device=dev)
+        indptr = i32([k * per for k in range(entries + 1)])
+        token_req = i32([r for r in range(entries) for _ in range(per)])
+        slot_sets = [i32([c * batch + k for k in range(entries)]) for c in range(copies)]
+        turn = {"i": 0}
+
+        def scan():
+            sl = slot_sets[turn["i"] % copies]
+            turn["i"] += 1
+            return ops.selective_scan(xc, xz, proj, w_dt, dt_bias, a_neg, d_skip, indptr, sl, state,
+                                      entries, inner, N, R, taps)
+
+        ms = _time_graph(scan, reps=max(copies, 4) if label == "decode" else 2)
+        nbytes = 2.0 * entries * size * 4 + tokens * (inner * 3 * 2 + (R + 2 * N) * 4.0)
+        record(f"selective_scan_{label}", ms, nbytes=nbytes,
+               tokens_per_chain_us=round(per / (ms * 1e3), 3))
+        ms = _time_graph(lambda: ops.conv_silu(xz, conv_w, conv_b, token_req, indptr, slot_sets[0],
+                                               state, inner, taps), reps=8)
+        record(f"conv_silu_{label}", ms, nbytes=tokens * inner * 4.0)
+
+    E, ident, top, ff = (moe["router"]["experts"], moe["router"]["identity"], moe["router"]["top"],
+                         moe["expert"]["ff"])
+    copies = max(1, -(-(160 << 20) // (E * 2 * ff * width * 2)))
+    w_up = [rnd(E * ff, width, scale=0.02) for _ in range(copies)]
+    w_dn = [rnd(E * width, ff, scale=0.02) for _ in range(copies)]
+    for tokens, label in ((batch, "decode"), (PROMPT_LEN, "prefill")):
+        x = rnd(tokens, width)
+        chosen, weight = ops.route_topk(torch.randn(tokens, E + ident, device=dev), top, softmax=True,
+                                        choice_bias=torch.zeros(E + ident, device=dev))
+        turn = {"i": 0}
+
+        def experts():
+            k = turn["i"] % copies
+            turn["i"] += 1
+            return ops.routed_experts(x, w_up[k], w_dn[k], chosen, weight, E, ff, False, gated=False,
+                                      identity=ident)
+
+        ms = _time_graph(experts, reps=max(copies * 2, 4) if label == "decode" else 2)
+        picks = [e for e in chosen.flatten().tolist() if e < E]
+        record(f"routed_experts_{label}", ms, nbytes=len(set(picks)) * 2.0 * ff * width * 2,
+               flops=2.0 * len(picks) * 2 * ff * width, experts_used=len(set(picks)))
+    for tokens, label in ((batch, "decode"), (PROMPT_LEN, "prefill")):
+        resid = torch.randn(tokens, width, device=dev)
+        a, b = rnd(tokens, width), rnd(tokens, width)
+        wa, wb = torch.randn(width, device=dev), torch.randn(width, device=dev)
+        ms = _time_graph(lambda: ops.mean_of_norms([a, b], [wa, wb], 1e-6), reps=20)
+        record(f"mean_of_norms_{label}", ms, nbytes=tokens * width * (2 + 2 + 4.0))
+        delta = torch.randn(tokens, width, device=dev)
+        ms = _time_graph(lambda: ops.add_postnorm_rmsnorm(resid, delta, wa, 1e-6, 0.0,
+                                                          out_dtype=torch.bfloat16, post_scale=0.5,
+                                                          plain_out=True), reps=20)
+        record(f"postnorm_add_{label}", ms, nbytes=tokens * width * (4 + 4 + 4 + 2.0))
     ops.check_error_word(dev)
     print(json.dumps(out))
     return 0
@@ -766,7 +973,7 @@ def main() -> int:
     ap.add_argument("--small", action="store_true", help="a smaller case, for profiler captures")
     ap.add_argument("--sizes", default="orpheus-3b", choices=sorted(SIZES),
                     help="layer sizes; the default is the benchmark model")
-    ap.add_argument("--arch", default=None, choices=["tifosun"],
+    ap.add_argument("--arch", default=None, choices=["tifosun", "vudivik"],
                     help="measure another architecture beside the Llama decoder at equal size "
                          "(prefill, decode, its own kernels) instead of the headline workload")
     ap.add_argument("--arch-size", default="small", choices=["small", "medium"])

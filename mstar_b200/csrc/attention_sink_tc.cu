@@ -1,0 +1,347 @@
+// The window attention with kept first keys (attention_sink.cu says what is computed) in
+// bfloat16 on the tensor cores, for prompt portions and decoded tokens alike.
+//
+// The rows of one (entry, kv head) are the pairs (token, query head of the group),
+// token-major; a CTA takes 64 consecutive rows (four warps of 16) and streams the keys and
+// values its rows can see through shared memory in tiles of 64 (cp.async, two stages).  The
+// keys a CTA visits are numbered without the gap: first the kept first keys that lie before
+// the window of its first row, then the keys from that window's start to its last row's
+// position; each row masks by its own position (j <= p and (p - j < window or j <
+// keep_first)).  S = Q K^T is an m16n8k16 MMA with float sums; the softmax is online and
+// float; the probabilities enter O += P V as three bfloat16 parts that together hold the
+// float exactly, so that the weights stay 32-bit; O is float.  Key and value sizes are
+// padded with zeros in shared memory to the next compiled size D.
+//
+// With few rows (decoding) the visited keys are shared among `splits` CTAs, each leaving an
+// unnormalised partial (o, running maximum, sum) in scratch, and a second kernel merges.
+#include "common.cuh"
+#include "mma_util.cuh"
+
+#define ST_THREADS 128
+#define ST_ROWS 64
+#define ST_TILE 64
+
+struct SinkTcArgs {
+    const bf16* q;
+    const bf16* kv;
+    const int* block_table;
+    const int* qo_indptr;
+    const int* kv_len;
+    bf16* out;
+    float* scratch;
+    int q_stride, bt_stride, nq, nkv, hd, vd, page_size, window, keep_first, splits;
+    float scale_log2e;
+};
+
+template <int D> __device__ __forceinline__ int st_off(int row, int c) { return row * (D + 8) + c * 8; }
+
+template <int D>
+__global__ void __launch_bounds__(ST_THREADS)
+sink_attention_tc_kernel(SinkTcArgs a) {
+    constexpr int CPR = D / 8;
+    constexpr int LD = D + 8;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* stages = reinterpret_cast<bf16*>(smem_raw);      // [2]{K [64][LD], V [64][LD]}
+    bf16* Qs = stages + 2 * 2 * ST_TILE * LD;              // [64][LD]
+
+    const int split = blockIdx.x % a.splits;
+    const int tile = gridDim.x / a.splits - 1 - blockIdx.x / a.splits;   // long tiles first
+    const int kvh = blockIdx.y, e = blockIdx.z;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int G = a.nq / a.nkv;
+    const unsigned long long waited = pdl_wait();
+    const bf16* q = pdl_after(a.q, waited);
+    const bf16* kv = pdl_after(a.kv, waited);
+    const int q_start = a.qo_indptr[e];
+    const int q_len = a.qo_indptr[e + 1] - q_start;
+    const int rows_total = q_len * G;
+    const int row0 = tile * ST_ROWS;
+    if (row0 >= rows_total) return;
+    const int past = a.kv_len[e] - q_len;      // cache position of the entry's first new token
+    const int W = a.window > 0 ? a.window : 0x3fffffff;
+    const int last_row = min(rows_total, row0 + ST_ROWS) - 1;
+    const int hi = past + last_row / G + 1;
+    const int lo = max(0, past + row0 / G - W + 1);
+    const int kept = min(a.keep_first, lo);    // kept first keys before the CTA's window
+    const int visible = kept + hi - lo;
+
+    const int* bt = a.block_table + (size_t)e * a.bt_stride;
+    const size_t page_elems = (size_t)a.nkv * a.page_size * (a.hd + a.vd);
+    const size_t k_head = (size_t)kvh * a.page_size * a.hd;
+    const size_t v_head = (size_t)a.nkv * a.page_size * a.hd + (size_t)kvh * a.page_size * a.vd;
+    const int kc = a.hd / 8, vc = a.vd / 8;    // 16-byte chunks of a real key / value row
+
+    for (int i = tid; i < ST_ROWS * CPR; i += ST_THREADS) {
+        const int r = i / CPR, c = i - r * CPR;
+        const int row = row0 + r;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (row < rows_total && c < kc) {
+            const int tok = q_start + row / G, head = kvh * G + row % G;
+            v = *reinterpret_cast<const uint4*>(q + (size_t)tok * a.q_stride + (size_t)head * a.hd + c * 8);
+        }
+        *reinterpret_cast<uint4*>(Qs + st_off<D>(r, c)) = v;
+    }
+    auto load_tile = [&](int stage, int base) {
+        bf16* Ks = stages + (size_t)stage * 2 * ST_TILE * LD;
+        bf16* Vs = Ks + ST_TILE * LD;
+        for (int i = tid; i < ST_TILE * CPR; i += ST_THREADS) {
+            const int r = i / CPR, c = i - r * CPR;
+            const int v = base + r;
+            const bool ok = v < visible;
+            const bf16* ksrc = kv;
+            const bf16* vsrc = kv;
+            if (ok) {
+                const int key = v < kept ? v : lo + v - kept;
+                const int pg = key / a.page_size;
+                const bf16* page = kv + (size_t)bt[pg] * page_elems;
+                const int slot = key - pg * a.page_size;
+                ksrc = page + k_head + (size_t)slot * a.hd + c * 8;
+                vsrc = page + v_head + (size_t)slot * a.vd + c * 8;
+            }
+            const int off = st_off<D>(r, c);
+            cp_async_16(smem_u32(Ks + off), ok && c < kc ? ksrc : kv, ok && c < kc ? 16 : 0);
+            cp_async_16(smem_u32(Vs + off), ok && c < vc ? vsrc : kv, ok && c < vc ? 16 : 0);
+        }
+    };
+
+    // this thread's two rows (g and g+8 of the warp's 16) and their positions
+    const int rowA = row0 + warp * 16 + (lane >> 2), rowB = rowA + 8;
+    const int cpA = past + min(rowA, rows_total - 1) / G;
+    const int cpB = past + min(rowB, rows_total - 1) / G;
+    // the warp's rows together: newest key any row sees, oldest window key any row sees
+    const int warp_hi = past + min(row0 + warp * 16 + 15, rows_total - 1) / G;
+    const int warp_lo = max(0, past + min(row0 + warp * 16, rows_total - 1) / G - W + 1);
+
+    float o[D / 8][4];
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+    const int ntiles_all = (visible + ST_TILE - 1) / ST_TILE;
+    const int per_split = (ntiles_all + a.splits - 1) / a.splits;
+    const int t_first = split * per_split;
+    const int ntiles = max(0, min(ntiles_all, t_first + per_split) - t_first);
+    if (ntiles > 0) load_tile(0, t_first * ST_TILE);
+    cp_async_commit();
+    for (int it = 0; it < ntiles; ++it) {
+        if (it + 1 < ntiles) load_tile((it + 1) & 1, (t_first + it + 1) * ST_TILE);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const bf16* Ks = stages + (size_t)(it & 1) * 2 * ST_TILE * LD;
+        const bf16* Vs = Ks + ST_TILE * LD;
+        const int base = (t_first + it) * ST_TILE;
+        // keys of the tile: kept first keys (always of interest), or window keys
+        const int key_first = base < kept ? base : lo + base - kept;
+        const int key_last = lo + min(base + ST_TILE, visible) - 1 - kept;
+        if (base < kept || (key_first <= warp_hi && key_last >= warp_lo)) {
+            float s[8][4];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+                uint32_t qa[4];
+                const int arow = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                ldmatrix_x4(qa, smem_u32(Qs + st_off<D>(arow, 2 * kk + (lane >> 4))));
+#pragma unroll
+                for (int jp = 0; jp < 4; ++jp) {
+                    uint32_t kb[4];
+                    const int brow = jp * 16 + (lane & 7) + (lane >> 4) * 8;
+                    ldmatrix_x4(kb, smem_u32(Ks + st_off<D>(brow, 2 * kk + ((lane >> 3) & 1))));
+                    mma_bf16_16816(s[2 * jp], qa, kb[0], kb[1]);
+                    mma_bf16_16816(s[2 * jp + 1], qa, kb[2], kb[3]);
+                }
+            }
+            float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const int v = base + j * 8 + (lane & 3) * 2 + (q4 & 1);
+                    const int key = v < kept ? v : lo + v - kept;
+                    const bool upper = q4 < 2;
+                    const int cp = upper ? cpA : cpB;
+                    const bool ok = v < visible && key <= cp && (cp - key < W || key < a.keep_first);
+                    const float sv = ok ? s[j][q4] * a.scale_log2e : -INFINITY;
+                    s[j][q4] = sv;
+                    if (upper) mx0 = fmaxf(mx0, sv); else mx1 = fmaxf(mx1, sv);
+                }
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+            const float b0 = mn0 == -INFINITY ? 0.f : mn0, b1 = mn1 == -INFINITY ? 0.f : mn1;
+            const float al0 = exp2f(m0 - b0), al1 = exp2f(m1 - b1);
+            m0 = mn0;
+            m1 = mn1;
+            float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                s[j][0] = exp2f(s[j][0] - b0);
+                s[j][1] = exp2f(s[j][1] - b0);
+                s[j][2] = exp2f(s[j][2] - b1);
+                s[j][3] = exp2f(s[j][3] - b1);
+                ps0 += s[j][0] + s[j][1];
+                ps1 += s[j][2] + s[j][3];
+            }
+            l0 = l0 * al0 + ps0;
+            l1 = l1 * al1 + ps1;
+#pragma unroll
+            for (int n = 0; n < D / 8; ++n) {
+                o[n][0] *= al0; o[n][1] *= al0; o[n][2] *= al1; o[n][3] *= al1;
+            }
+            // O += P V with P = P1 + P2 + P3, three bfloat16 parts that hold the float exactly
+#pragma unroll
+            for (int part = 0; part < 3; ++part) {
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    uint32_t pa[4];
+                    pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+                    pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+                    pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+                    pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+                    if (part < 2) {            // what the parts so far leave
+#pragma unroll
+                        for (int jj = 0; jj < 2; ++jj)
+#pragma unroll
+                            for (int q4 = 0; q4 < 4; ++q4)
+                                s[2 * kk + jj][q4] -= __bfloat162float(__float2bfloat16_rn(s[2 * kk + jj][q4]));
+                    }
+#pragma unroll
+                    for (int n2 = 0; n2 < D / 16; ++n2) {
+                        uint32_t vb[4];
+                        const int vrow = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                        ldmatrix_x4_trans(vb, smem_u32(Vs + st_off<D>(vrow, 2 * n2 + (lane >> 4))));
+                        mma_bf16_16816(o[2 * n2], pa, vb[0], vb[1]);
+                        mma_bf16_16816(o[2 * n2 + 1], pa, vb[2], vb[3]);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int row = half ? rowB : rowA;
+        if (row >= rows_total) continue;
+        const float l = half ? l1 : l0, m = half ? m1 : m0;
+        const int tok = q_start + row / G, head = kvh * G + row % G;
+        if (a.splits == 1) {
+            const float inv = 1.f / l;
+            bf16* dst = a.out + ((size_t)tok * a.nq + head) * a.vd + (lane & 3) * 2;
+#pragma unroll
+            for (int n = 0; n < D / 8; ++n)
+                if (n * 8 < a.vd)
+                    *reinterpret_cast<__nv_bfloat162*>(dst + n * 8) =
+                        __floats2bfloat162_rn(o[n][2 * half] * inv, o[n][2 * half + 1] * inv);
+        } else {
+            float* dst = a.scratch + (((size_t)tok * a.nq + head) * a.splits + split) * (a.vd + 2);
+#pragma unroll
+            for (int n = 0; n < D / 8; ++n)
+                if (n * 8 < a.vd) {
+                    dst[n * 8 + (lane & 3) * 2] = o[n][2 * half];
+                    dst[n * 8 + (lane & 3) * 2 + 1] = o[n][2 * half + 1];
+                }
+            if ((lane & 3) == 0) {
+                dst[a.vd] = m;
+                dst[a.vd + 1] = l;
+            }
+        }
+    }
+}
+
+// One warp per (token, head): the partials of the splits, weighted by 2^(m_s - max m).
+__global__ void sink_merge_kernel(const float* __restrict__ scratch, bf16* __restrict__ out,
+                                  int rows, int vd, int splits) {
+    scratch = pdl_after(scratch, pdl_wait());
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const float* base = scratch + (size_t)row * splits * (vd + 2);
+    float M = -INFINITY;
+    for (int s = 0; s < splits; ++s) M = fmaxf(M, base[(size_t)s * (vd + 2) + vd]);
+    float L = 0.f;
+    for (int s = 0; s < splits; ++s) {
+        const float* p = base + (size_t)s * (vd + 2);
+        L += p[vd + 1] * exp2f(p[vd] - M);
+    }
+    for (int d = lane; d < vd; d += 32) {
+        float sum = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float* p = base + (size_t)s * (vd + 2);
+            sum += p[d] * exp2f(p[vd] - M);
+        }
+        out[(size_t)row * vd + d] = __float2bfloat16_rn(sum / L);
+    }
+}
+
+template <int D>
+static int launch_sink_tc(const SinkTcArgs& a, int entries, int max_q_len, cudaStream_t s) {
+    const size_t smem = (size_t)5 * ST_TILE * (D + 8) * sizeof(bf16);
+    static bool configured = false;
+    if (!configured && smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(sink_attention_tc_kernel<D>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const int G = a.nq / a.nkv;
+    const long long tiles = ((long long)max_q_len * G + ST_ROWS - 1) / ST_ROWS;
+    if (tiles * a.splits > 2147483647LL) return -1;
+    dim3 grid((unsigned)(tiles * a.splits), a.nkv, entries);
+    mstar_launch((sink_attention_tc_kernel<D>), grid, dim3(ST_THREADS), smem, s, a);
+    return launch_status();
+}
+
+// Entries [0, entries) of the batch; q: [tokens] rows of q_stride elements; out: [tokens,
+// nq * vd]; scratch: float [tokens * nq * splits * (vd + 2)] when splits > 1.  Returns 0, a
+// CUDA error code, or -1 when the shape is refused (sizes no multiples of 8 or above 256).
+MSTAR_API int mstar_sink_attention_tc(const void* q, int q_stride, void* out, const void* kv_cache,
+                                      const int* block_table, int bt_stride, const int* qo_indptr,
+                                      const int* kv_len, int entries, int tokens, int max_q_len,
+                                      int nq, int nkv, int hd, int vd, int page_size, int window,
+                                      int keep_first, float scale, int splits, float* scratch,
+                                      void* stream) {
+    if (entries <= 0 || max_q_len <= 0) return 0;
+    if (nkv <= 0 || nq % nkv != 0 || entries > 65535 || nkv > 65535) return -1;
+    if (hd % 8 || vd % 8 || hd <= 0 || vd <= 0 || hd > 256 || vd > 256 || splits < 1) return -1;
+    if (splits > 1 && scratch == nullptr) return -1;
+    SinkTcArgs a;
+    a.q = (const bf16*)q;
+    a.kv = (const bf16*)kv_cache;
+    a.block_table = block_table;
+    a.qo_indptr = qo_indptr;
+    a.kv_len = kv_len;
+    a.out = (bf16*)out;
+    a.scratch = scratch;
+    a.q_stride = q_stride;
+    a.bt_stride = bt_stride;
+    a.nq = nq;
+    a.nkv = nkv;
+    a.hd = hd;
+    a.vd = vd;
+    a.page_size = page_size;
+    a.window = window;
+    a.keep_first = window > 0 ? keep_first : 0;
+    a.splits = splits;
+    a.scale_log2e = scale * 1.4426950408889634f;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int wide = hd > vd ? hd : vd;
+    int code;
+    if (wide <= 32) code = launch_sink_tc<32>(a, entries, max_q_len, s);
+    else if (wide <= 64) code = launch_sink_tc<64>(a, entries, max_q_len, s);
+    else if (wide <= 96) code = launch_sink_tc<96>(a, entries, max_q_len, s);
+    else if (wide <= 128) code = launch_sink_tc<128>(a, entries, max_q_len, s);
+    else code = launch_sink_tc<256>(a, entries, max_q_len, s);
+    if (code != 0 || splits == 1) return code;
+    const int rows = tokens * nq;
+    mstar_launch(sink_merge_kernel, dim3((rows + 3) / 4), dim3(128), 0, s, (const float*)scratch,
+                 (bf16*)out, rows, vd, splits);
+    return launch_status();
+}

@@ -1094,16 +1094,57 @@ def sink_prepare(qkv: torch.Tensor, bias, q_norm, k_norm, freq, positions, cache
     return q
 
 
+def sink_attention_splits(entries: int, max_q_len: int, num_heads: int, num_kv_heads: int,
+                          max_keys: int, sms: int | None = None) -> int:
+    """Among how many CTAs the keys of a row tile are shared in the tensor-core kernel: one
+    where the row tiles alone fill the GPU, else enough for some two CTAs per SM, a split
+    keeping at least two tiles of 64 keys."""
+    if sms is None:
+        sms = num_sms()
+    group = num_heads // num_kv_heads
+    ctas = max(1, -(-max_q_len * group // 64) * num_kv_heads * entries)
+    if ctas >= sms:
+        return 1
+    return max(1, min(-(-2 * sms // ctas), -(-max_keys // 64) // 2, 64))
+
+
 def sink_attention(q: torch.Tensor, kv_cache: torch.Tensor, block_table, token_req, cache_pos,
                    num_heads: int, num_kv_heads: int, head_dim: int, v_dim: int, page_size: int,
                    window: int, keep_first: int, scale: float, ctx=None) -> torch.Tensor:
     """Softmax attention of every token over the keys it sees: those of the last ``window``
     positions (0: all) and the first ``keep_first`` of the sequence.  ``q``: [tokens, heads *
-    head_dim]; returns [tokens, heads * v_dim]."""
+    head_dim]; returns [tokens, heads * v_dim].  bfloat16 with sizes that are multiples of 8
+    up to 256 and a step context (``ctx``: entries, their token ranges and lengths) runs on
+    the tensor cores (MSTAR_SINK_ATTENTION=generic: never); everything else, float32
+    included, on the CUDA cores."""
     _need_cuda(q, kv_cache, block_table, token_req, cache_pos)
     assert q.is_contiguous() and kv_cache.is_contiguous() and kv_cache.dtype == q.dtype
     tokens = q.shape[0]
     out = torch.empty((tokens, num_heads * v_dim), dtype=q.dtype, device=q.device)
+    if (ctx is not None and q.dtype == torch.bfloat16 and head_dim % 8 == 0 and v_dim % 8 == 0
+            and max(head_dim, v_dim) <= 256 and os.environ.get("MSTAR_SINK_ATTENTION") != "generic"):
+        max_keys = ctx.max_kv_len
+        if window:
+            max_keys = min(max_keys, window + keep_first + ctx.max_q_len)
+        splits = sink_attention_splits(ctx.num_entries, ctx.max_q_len, num_heads, num_kv_heads,
+                                       max_keys, num_sms(q.device))
+        scratch = None
+        if splits > 1:
+            scratch = torch.empty(tokens * num_heads * splits * (v_dim + 2), dtype=torch.float32,
+                                  device=q.device)
+        code = lib.get("attention_sink_tc").mstar_sink_attention_tc(
+            q.data_ptr(), q.stride(0), out.data_ptr(), kv_cache.data_ptr(), block_table.data_ptr(),
+            block_table.stride(0), ctx.qo_indptr.data_ptr(), ctx.kv_len.data_ptr(),
+            ctx.num_entries, tokens, ctx.max_q_len, num_heads, num_kv_heads, head_dim, v_dim,
+            page_size, int(window or 0), int(keep_first), float(scale), splits, _ptr(scratch),
+            _stream())
+        if code == -1:
+            raise KernelError(f"tensor-core window attention refuses heads={num_heads}, "
+                              f"kv_heads={num_kv_heads}, head_dim={head_dim}, v_dim={v_dim}")
+        check(code, "sink_attention_tc")
+        if splits > 1:
+            lib.add_launches(1)                 # the merge kernel
+        return out
     code = lib.get("attention_sink").mstar_sink_attention_generic(
         q.data_ptr(), q.stride(0), out.data_ptr(), kv_cache.data_ptr(), block_table.data_ptr(),
         block_table.stride(0), token_req.data_ptr(), cache_pos.data_ptr(), tokens, num_heads,

@@ -45,6 +45,7 @@ LIBRARIES = {
     "attention_latent": ("cuda", ["attention_latent.cu"], []),
     "routed_experts": ("cuda", ["routed_experts.cu"], []),
     "attention_sink": ("cuda", ["attention_sink.cu"], []),
+    "attention_sink_tc": ("cuda", ["attention_sink_tc.cu"], []),
     "selective_scan": ("cuda", ["selective_scan.cu"], []),
     "host": ("host", ["host/cache_manager.cpp"], []),
 }

@@ -58,6 +58,10 @@ _SIGNATURES = {
         "mstar_sink_attention_generic": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i,
                                          _i, _i, _i, _f, _i, _vp],
     },
+    "attention_sink_tc": {
+        "mstar_sink_attention_tc": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i,
+                                    _i, _i, _i, _i, _f, _i, _vp, _vp],
+    },
     "selective_scan": {
         "mstar_conv_silu": [_vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i,
                             _vp],

@@ -212,9 +212,9 @@ def _sub(tensors, prefix):
 def plain_layer(x, tensors, config, i, state):
     """One run of layer i on the rows x; returns the new residual."""
     layer = config["layers"][i]
-    owner = layer.get("weights_of", i)
-    if owner is None:
-        owner = i
+    owner = i
+    while config["layers"][owner].get("weights_of") is not None:
+        owner = config["layers"][owner]["weights_of"]
     eps, m = config["norm"]["eps"], config["residual_mult"]
     if layer["type"] != "parallel":
         raise ValueError(layer["type"])

@@ -79,9 +79,11 @@ MIXED = config([
 ])
 
 
-def random_weights(cfg: dict, seed: int, sharp: float = 3.0) -> dict:
+def random_weights(cfg: dict, seed: int, sharp: float = 1.5) -> dict:
     """Checkpoint tensors (bfloat16 values).  Projections keep activations of order one; the
-    query and key norm weights are ``sharp`` so that a query's weight lies on a few keys;
+    query and key norm weights are ``sharp`` (at 3 a query's weight lies on a few keys, which
+    the tests of the attention alone use; whole models take less, or seven layers of such
+    attention amplify the rounding of bfloat16 activations beyond any use as a yardstick);
     step sizes of the scan spread over two decades and its decays over one."""
     g = torch.Generator().manual_seed(seed)
     w: dict = {}
