@@ -683,7 +683,7 @@ def vudivik_bench(args) -> int:
             sl = slot_sets[turn["i"] % copies]
             turn["i"] += 1
             return ops.selective_scan(xc, xz, proj, w_dt, dt_bias, a_neg, d_skip, indptr, sl, state,
-                                      entries, inner, N, R, taps)
+                                      entries, inner, N, R, taps, max_q_len=per)
 
         ms = _time_graph(scan, reps=max(copies, 4) if label == "decode" else 2)
         nbytes = 2.0 * entries * size * 4 + tokens * (inner * 3 * 2 + (R + 2 * N) * 4.0)

@@ -23,7 +23,7 @@ struct PrepArgs {
 };
 
 // One block per token.  Sines and cosines of the token's angles are made once (double
-// precision product and sincos) and shared by all heads.
+// precision product) and shared by all heads.
 template <typename A, typename W>
 __global__ void __launch_bounds__(256)
 sink_prepare_kernel(const float* __restrict__ qkv, const W* __restrict__ bias,
@@ -40,12 +40,16 @@ sink_prepare_kernel(const float* __restrict__ qkv, const W* __restrict__ bias,
     const int nwarps = blockDim.x >> 5;
     const unsigned long long waited = pdl_wait();
     qkv = pdl_after(qkv, waited);
+    // the angle in double precision, brought into [-pi, pi] there; sine and cosine of that
+    // in float (the argument is then exact to 2e-7 whatever the position)
     const double pos = (double)positions[t];
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
-        double s, c;
-        sincos(pos * freq[i], &s, &c);
-        cs[i] = (float)c;
-        cs[half + i] = (float)s;
+        double ang = pos * freq[i];
+        ang -= 6.283185307179586476925 * rint(ang * 0.15915494309189533577);
+        float s, c;
+        sincosf((float)ang, &s, &c);
+        cs[i] = c;
+        cs[half + i] = s;
     }
     __syncthreads();
     const int row_len = (a.nq + a.nkv) * a.hd + a.nkv * a.vd;

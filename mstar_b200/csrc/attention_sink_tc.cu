@@ -35,14 +35,16 @@ struct SinkTcArgs {
 
 template <int D> __device__ __forceinline__ int st_off(int row, int c) { return row * (D + 8) + c * 8; }
 
-template <int D>
+// NSTAGE key/value tiles are in flight: two where rows are many (the tensor cores set the
+// pace), four where they are few (decoding: the latency of the copies does).
+template <int D, int NSTAGE>
 __global__ void __launch_bounds__(ST_THREADS)
 sink_attention_tc_kernel(SinkTcArgs a) {
     constexpr int CPR = D / 8;
     constexpr int LD = D + 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    bf16* stages = reinterpret_cast<bf16*>(smem_raw);      // [2]{K [64][LD], V [64][LD]}
-    bf16* Qs = stages + 2 * 2 * ST_TILE * LD;              // [64][LD]
+    bf16* stages = reinterpret_cast<bf16*>(smem_raw);      // [NSTAGE]{K [64][LD], V [64][LD]}
+    bf16* Qs = stages + NSTAGE * 2 * ST_TILE * LD;         // [64][LD]
 
     const int split = blockIdx.x % a.splits;
     const int tile = gridDim.x / a.splits - 1 - blockIdx.x / a.splits;   // long tiles first
@@ -121,20 +123,27 @@ sink_attention_tc_kernel(SinkTcArgs a) {
     const int per_split = (ntiles_all + a.splits - 1) / a.splits;
     const int t_first = split * per_split;
     const int ntiles = max(0, min(ntiles_all, t_first + per_split) - t_first);
-    if (ntiles > 0) load_tile(0, t_first * ST_TILE);
-    cp_async_commit();
-    for (int it = 0; it < ntiles; ++it) {
-        if (it + 1 < ntiles) load_tile((it + 1) & 1, (t_first + it + 1) * ST_TILE);
+#pragma unroll
+    for (int st = 0; st < NSTAGE - 1; ++st) {
+        if (st < ntiles) load_tile(st, (t_first + st) * ST_TILE);
         cp_async_commit();
-        cp_async_wait<1>();
+    }
+#pragma unroll 1
+    for (int it = 0; it < ntiles; ++it) {
+        const int ahead = it + NSTAGE - 1;
+        if (ahead < ntiles) load_tile(ahead % NSTAGE, (t_first + ahead) * ST_TILE);
+        cp_async_commit();
+        cp_async_wait<NSTAGE - 1>();
         __syncthreads();
-        const bf16* Ks = stages + (size_t)(it & 1) * 2 * ST_TILE * LD;
+        const bf16* Ks = stages + (size_t)(it % NSTAGE) * 2 * ST_TILE * LD;
         const bf16* Vs = Ks + ST_TILE * LD;
         const int base = (t_first + it) * ST_TILE;
         // keys of the tile: kept first keys (always of interest), or window keys
         const int key_first = base < kept ? base : lo + base - kept;
         const int key_last = lo + min(base + ST_TILE, visible) - 1 - kept;
-        if (base < kept || (key_first <= warp_hi && key_last >= warp_lo)) {
+        // (a warp whose rows all lie past the entry's last row has nothing to do)
+        if (row0 + warp * 16 < rows_total &&
+            (base < kept || (key_first <= warp_hi && key_last >= warp_lo))) {
             float s[8][4];
 #pragma unroll
             for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
@@ -192,7 +201,7 @@ sink_attention_tc_kernel(SinkTcArgs a) {
                 o[n][0] *= al0; o[n][1] *= al0; o[n][2] *= al1; o[n][3] *= al1;
             }
             // O += P V with P = P1 + P2 + P3, three bfloat16 parts that hold the float exactly
-#pragma unroll
+#pragma unroll 1
             for (int part = 0; part < 3; ++part) {
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk) {
@@ -257,36 +266,46 @@ sink_attention_tc_kernel(SinkTcArgs a) {
     }
 }
 
-// One warp per (token, head): the partials of the splits, weighted by 2^(m_s - max m).
+// One warp per (token, head): the partials of the splits, weighted by 2^(m_s - max m).  Lane s
+// fetches the maximum and the sum of split s (at most 64 splits: two a lane), the weights go
+// round by shuffles, and every lane sums its features over the splits with the loads of all
+// splits in flight together.
 __global__ void sink_merge_kernel(const float* __restrict__ scratch, bf16* __restrict__ out,
                                   int rows, int vd, int splits) {
     scratch = pdl_after(scratch, pdl_wait());
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (row >= rows) return;
     const float* base = scratch + (size_t)row * splits * (vd + 2);
-    float M = -INFINITY;
-    for (int s = 0; s < splits; ++s) M = fmaxf(M, base[(size_t)s * (vd + 2) + vd]);
-    float L = 0.f;
-    for (int s = 0; s < splits; ++s) {
-        const float* p = base + (size_t)s * (vd + 2);
-        L += p[vd + 1] * exp2f(p[vd] - M);
+    float m_a = -INFINITY, l_a = 0.f, m_b = -INFINITY, l_b = 0.f;
+    if (lane < splits) {
+        m_a = base[(size_t)lane * (vd + 2) + vd];
+        l_a = base[(size_t)lane * (vd + 2) + vd + 1];
     }
-    for (int d = lane; d < vd; d += 32) {
+    if (lane + 32 < splits) {
+        m_b = base[(size_t)(lane + 32) * (vd + 2) + vd];
+        l_b = base[(size_t)(lane + 32) * (vd + 2) + vd + 1];
+    }
+    const float M = warp_max(fmaxf(m_a, m_b));
+    const float w_a = exp2f(m_a - M), w_b = exp2f(m_b - M);   // 0 for a split that saw no key
+    const float L = warp_sum(l_a * w_a + l_b * w_b);
+    for (int d0 = 0; d0 < vd; d0 += 32) {
+        const int d = d0 + lane;
         float sum = 0.f;
+#pragma unroll 8
         for (int s = 0; s < splits; ++s) {
-            const float* p = base + (size_t)s * (vd + 2);
-            sum += p[d] * exp2f(p[vd] - M);
+            const float w = __shfl_sync(0xffffffffu, s < 32 ? w_a : w_b, s & 31);
+            if (d < vd) sum = fmaf(base[(size_t)s * (vd + 2) + d], w, sum);
         }
-        out[(size_t)row * vd + d] = __float2bfloat16_rn(sum / L);
+        if (d < vd) out[(size_t)row * vd + d] = __float2bfloat16_rn(sum / L);
     }
 }
 
-template <int D>
-static int launch_sink_tc(const SinkTcArgs& a, int entries, int max_q_len, cudaStream_t s) {
-    const size_t smem = (size_t)5 * ST_TILE * (D + 8) * sizeof(bf16);
+template <int D, int NSTAGE>
+static int launch_sink_tc_stages(const SinkTcArgs& a, int entries, int max_q_len, cudaStream_t s) {
+    const size_t smem = (size_t)(2 * NSTAGE + 1) * ST_TILE * (D + 8) * sizeof(bf16);
     static bool configured = false;
     if (!configured && smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(sink_attention_tc_kernel<D>,
+        cudaError_t e = cudaFuncSetAttribute(sink_attention_tc_kernel<D, NSTAGE>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
@@ -295,8 +314,18 @@ static int launch_sink_tc(const SinkTcArgs& a, int entries, int max_q_len, cudaS
     const long long tiles = ((long long)max_q_len * G + ST_ROWS - 1) / ST_ROWS;
     if (tiles * a.splits > 2147483647LL) return -1;
     dim3 grid((unsigned)(tiles * a.splits), a.nkv, entries);
-    mstar_launch((sink_attention_tc_kernel<D>), grid, dim3(ST_THREADS), smem, s, a);
+    mstar_launch((sink_attention_tc_kernel<D, NSTAGE>), grid, dim3(ST_THREADS), smem, s, a);
     return launch_status();
+}
+
+template <int D>
+static int launch_sink_tc(const SinkTcArgs& a, int entries, int max_q_len, cudaStream_t s) {
+    // one row tile per (entry, kv head): few rows, deep prefetch (where shared memory has room)
+    const bool few = (long long)max_q_len * (a.nq / a.nkv) <= ST_ROWS;
+    if constexpr (D <= 128) {
+        if (few) return launch_sink_tc_stages<D, 4>(a, entries, max_q_len, s);
+    }
+    return launch_sink_tc_stages<D, 2>(a, entries, max_q_len, s);
 }
 
 // Entries [0, entries) of the batch; q: [tokens] rows of q_stride elements; out: [tokens,
@@ -310,7 +339,8 @@ MSTAR_API int mstar_sink_attention_tc(const void* q, int q_stride, void* out, co
                                       void* stream) {
     if (entries <= 0 || max_q_len <= 0) return 0;
     if (nkv <= 0 || nq % nkv != 0 || entries > 65535 || nkv > 65535) return -1;
-    if (hd % 8 || vd % 8 || hd <= 0 || vd <= 0 || hd > 256 || vd > 256 || splits < 1) return -1;
+    if (hd % 8 || vd % 8 || hd <= 0 || vd <= 0 || hd > 256 || vd > 256 || splits < 1 || splits > 64)
+        return -1;
     if (splits > 1 && scratch == nullptr) return -1;
     SinkTcArgs a;
     a.q = (const bf16*)q;

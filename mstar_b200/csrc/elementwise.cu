@@ -641,6 +641,68 @@ MSTAR_API int mstar_mean_of_norms(const void* x0, const void* x1, const void* x2
     return launch_status();
 }
 
+// ------------------------------------- mean of two normed branches + post-norm + residual add
+//   y      = (rms(x0) * w0 + rms(x1) * w1) / 2
+//   resid += post_scale * rms(y, post_eps) * (post_w + post_off)
+//   out    = resid in the activation type (when out != nullptr)
+// One block per row; y stays in shared memory.  All sums and scales are float.
+template <typename A>
+__global__ void mean2_postnorm_kernel(float* __restrict__ resid, const A* __restrict__ x0,
+                                      const A* __restrict__ x1, const float* __restrict__ w0,
+                                      const float* __restrict__ w1, float eps,
+                                      const float* __restrict__ post_w, float post_eps,
+                                      float post_off, float post_scale, A* __restrict__ out,
+                                      int hidden) {
+    extern __shared__ float row[];           // [2][hidden]: the branches, then y in the first
+    __shared__ float scratch[32];
+    const size_t base = (size_t)blockIdx.x * hidden;
+    const unsigned long long waited = pdl_wait();
+    x0 = pdl_after(x0, waited);
+    x1 = pdl_after(x1, waited);
+    float s0 = 0.f, s1 = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float a = to_float(x0[base + i]), b = to_float(x1[base + i]);
+        row[i] = a;
+        row[hidden + i] = b;
+        s0 = fmaf(a, a, s0);
+        s1 = fmaf(b, b, s1);
+    }
+    const float inv0 = rsqrtf(block_sum(s0, scratch) / (float)hidden + eps);
+    const float inv1 = rsqrtf(block_sum(s1, scratch) / (float)hidden + eps);
+    float sy = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float y = (row[i] * inv0 * w0[i] + row[hidden + i] * inv1 * w1[i]) * 0.5f;
+        row[i] = y;
+        sy = fmaf(y, y, sy);
+    }
+    const float invy = rsqrtf(block_sum(sy, scratch) / (float)hidden + post_eps);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float h = resid[base + i] + post_scale * (row[i] * invy * (post_w[i] + post_off));
+        resid[base + i] = h;
+        if (out != nullptr) out[base + i] = from_float<A>(h);
+    }
+}
+
+MSTAR_API int mstar_mean2_postnorm(float* resid, const void* x0, const void* x1, const float* w0,
+                                   const float* w1, float eps, const float* post_w, float post_eps,
+                                   float post_off, float post_scale, void* out, int act_dtype,
+                                   int rows, int hidden, void* stream) {
+    if (rows <= 0) return 0;
+    if (hidden <= 0 || hidden > 48 * 1024 / 8) return -1;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    const size_t smem = sizeof(float) * 2 * (size_t)hidden;
+    if (act_dtype == MSTAR_F32)
+        mstar_launch((mean2_postnorm_kernel<float>), dim3(rows), dim3(threads), smem, s, resid,
+                     (const float*)x0, (const float*)x1, w0, w1, eps, post_w, post_eps, post_off,
+                     post_scale, (float*)out, hidden);
+    else
+        mstar_launch((mean2_postnorm_kernel<bf16>), dim3(rows), dim3(threads), smem, s, resid,
+                     (const bf16*)x0, (const bf16*)x1, w0, w1, eps, post_w, post_eps, post_off,
+                     post_scale, (bf16*)out, hidden);
+    return launch_status();
+}
+
 // ------------------------------------------------------------ activations without a gate
 // kind 0: relu(x)^2, 1: gelu (tanh form), 2: silu.  In place or not.
 __device__ __forceinline__ float plain_activation(float v, int kind) {

@@ -715,6 +715,14 @@ def add_postnorm_rmsnorm(resid: torch.Tensor, delta: torch.Tensor, post_weight: 
     ``plain_out`` (and no weight), returns the new residual itself in ``out_dtype`` (the
     residual tensor when that is float); else None.  ``post_weight`` is a float vector;
     ``delta`` is float or of ``out_dtype``."""
+    if isinstance(delta, MeanOfNorms):
+        # the mean of two normed branches that nobody has computed yet: one kernel does it
+        # together with this norm and the sum, where it has a form for the case
+        fused = delta.fused_postnorm(resid, post_weight, post_eps, post_offset, post_scale,
+                                     weight, out_dtype, plain_out)
+        if fused is not NotImplemented:
+            return fused
+        delta = delta.materialize()
     _need_cuda(resid, delta, post_weight, weight)
     assert resid.dtype == torch.float32 and resid.dim() == 2 and resid.is_contiguous()
     assert delta.shape == resid.shape and delta.is_contiguous()
@@ -758,6 +766,47 @@ def mean_of_norms(branches, weights, eps: float) -> torch.Tensor:
         *xs, *ws, n, out.data_ptr(), _dt(branches[0]), rows, hidden, float(eps), _stream()),
         "mean_of_norms")
     return out
+
+
+class MeanOfNorms:
+    """The mean of normed branch outputs, not computed yet: ``materialize()`` runs
+    ``mean_of_norms``; a norm that is to add it to the residual may take the two steps as one
+    kernel (``add_postnorm_rmsnorm`` does for two branches)."""
+
+    def __init__(self, branches, weights, eps: float):
+        self.branches, self.weights, self.eps = list(branches), list(weights), float(eps)
+        self.shape, self.dtype = branches[0].shape, torch.float32
+
+    def materialize(self) -> torch.Tensor:
+        return mean_of_norms(self.branches, self.weights, self.eps)
+
+    def fused_postnorm(self, resid, post_weight, post_eps, post_offset, post_scale, weight,
+                       out_dtype, plain_out):
+        x0 = self.branches[0]
+        hidden = resid.shape[1]
+        if (len(self.branches) != 2 or weight is not None or hidden > 6144
+                or os.environ.get("MSTAR_FUSED_MEAN") == "0"):
+            return NotImplemented
+        out_dtype = out_dtype or x0.dtype
+        if out_dtype != x0.dtype:
+            return NotImplemented
+        _need_cuda(resid, *self.branches, *self.weights, post_weight)
+        assert resid.dtype == torch.float32 and resid.is_contiguous() and resid.shape == x0.shape
+        assert post_weight.dtype == torch.float32 and post_weight.numel() == hidden
+        for x, w in zip(self.branches, self.weights):
+            assert x.shape == x0.shape and x.dtype == x0.dtype and x.is_contiguous()
+            assert w.dtype == torch.float32 and w.numel() == hidden
+        out = None
+        if plain_out and out_dtype != torch.float32:
+            out = torch.empty(resid.shape, dtype=out_dtype, device=resid.device)
+        check(lib.get("elementwise").mstar_mean2_postnorm(
+            resid.data_ptr(), x0.data_ptr(), self.branches[1].data_ptr(),
+            self.weights[0].data_ptr(), self.weights[1].data_ptr(), self.eps,
+            post_weight.data_ptr(), float(post_eps), float(post_offset), float(post_scale),
+            _ptr(out), _dt(x0), resid.shape[0], hidden, _stream()), "mean2_postnorm")
+        if plain_out and out is None:
+            return resid
+        return out
 
 
 ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2}
@@ -1183,15 +1232,26 @@ def conv_silu(xz: torch.Tensor, weight, bias, token_req, qo_indptr, slots, state
     return out
 
 
+# Tokens of a piece when a long portion's recurrence is cut into pieces that run side by side
+# (a multiple of the kernel's chunk of 16), and the portion length from which on it is cut.
+SCAN_PIECE = 128
+SCAN_PIECES_FROM = 512
+
+
 def selective_scan(xc: torch.Tensor, xz: torch.Tensor, proj: torch.Tensor, w_dt, dt_bias, a_neg,
                    d_skip, qo_indptr, slots, state: torch.Tensor, entries: int, inner: int,
-                   n_state: int, rank: int, taps: int) -> torch.Tensor:
+                   n_state: int, rank: int, taps: int, max_q_len: int | None = None) -> torch.Tensor:
     """The recurrence over the tokens of ``entries`` batch entries, each continuing the state
     in its slot (S updated in place, the convolution's window moved on by the portion).
     ``xc`` [tokens, inner] conv outputs; ``xz`` [tokens, 2 * inner] (the gate z is its second
     half, the raw x its first); ``proj`` float [tokens, rank + 2 * n_state] = [dt_in | B | C];
     float ``w_dt`` [inner, rank], ``dt_bias`` [inner], ``a_neg`` [inner, n_state] (= -exp(A_log)),
-    ``d_skip`` [inner].  Returns y * silu(z) [tokens, inner] in the dtype of ``xc``."""
+    ``d_skip`` [inner].  Returns y * silu(z) [tokens, inner] in the dtype of ``xc``.
+    ``max_q_len`` (the longest portion of the batch) of ``SCAN_PIECES_FROM`` tokens or more
+    cuts every portion into pieces of ``SCAN_PIECE`` tokens that run side by side: a first
+    pass leaves each piece's own end state and summed step sizes, a second starts each piece
+    from the state joined over the pieces before it (the recurrence is linear in the state);
+    MSTAR_SCAN_PIECE sets another piece size, 0 none."""
     _need_cuda(xc, xz, proj, w_dt, dt_bias, a_neg, d_skip, qo_indptr, slots, state)
     assert xc.is_contiguous() and xz.stride(1) == 1 and xz.dtype == xc.dtype
     assert proj.dtype == torch.float32 and proj.is_contiguous()
@@ -1202,11 +1262,21 @@ def selective_scan(xc: torch.Tensor, xz: torch.Tensor, proj: torch.Tensor, w_dt,
     assert state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1
     assert state.shape[1] == selective_scan_state_size(inner, n_state, taps)
     out = torch.empty_like(xc)
+    piece, pieces, piece_state, piece_dt = 0, 1, None, None
+    if max_q_len is not None and max_q_len >= SCAN_PIECES_FROM:
+        piece = int(os.environ.get("MSTAR_SCAN_PIECE", SCAN_PIECE)) // 16 * 16
+    if piece:
+        pieces = -(-max_q_len // piece)
+        piece_state = torch.empty((entries, pieces, inner, n_state), dtype=torch.float32,
+                                  device=xc.device)
+        piece_dt = torch.empty((entries, pieces, inner), dtype=torch.float32, device=xc.device)
     code = lib.get("selective_scan").mstar_selective_scan(
         xc.data_ptr(), xz.data_ptr(), xz.stride(0), proj.data_ptr(), w_dt.data_ptr(),
         dt_bias.data_ptr(), a_neg.data_ptr(), d_skip.data_ptr(), qo_indptr.data_ptr(),
         slots.data_ptr(), state.data_ptr(), state.stride(0), out.data_ptr(), _dt(xc), entries,
-        inner, n_state, rank, taps, _stream())
+        inner, n_state, rank, taps, piece, pieces, _ptr(piece_state), _ptr(piece_dt), _stream())
+    if piece:
+        lib.add_launches(1)                     # two passes behind one call
     if code == -1:
         raise KernelError(f"selective scan refuses inner={inner}, state={n_state}, rank={rank} "
                           "(at most 256 states a channel)")

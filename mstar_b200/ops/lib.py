@@ -32,6 +32,8 @@ _SIGNATURES = {
         "mstar_mean_of_norms": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _f,
                                 _vp],
         "mstar_activation": [_vp, _vp, _i, _ll, _i, _vp],
+        "mstar_mean2_postnorm": [_vp, _vp, _vp, _vp, _vp, _f, _vp, _f, _f, _f, _vp, _i, _i, _i,
+                                 _vp],
         "mstar_sigmoid_gate_mul": [_vp, _vp, _i, _i, _i, _i, _vp],
     },
     "matrix_memory": {
@@ -66,7 +68,7 @@ _SIGNATURES = {
         "mstar_conv_silu": [_vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i,
                             _vp],
         "mstar_selective_scan": [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _vp,
-                                 _i, _i, _i, _i, _i, _i, _vp],
+                                 _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp],
     },
     "attention_generic": {
         "mstar_paged_attention_generic": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i,

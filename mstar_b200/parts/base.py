@@ -119,6 +119,8 @@ class ResidualStream:
         if self.post is not None:
             self.settle()
         d, self.delta = self.delta, None
+        if hasattr(d, "materialize"):           # a part's output that is not computed yet
+            d = d.materialize()
         return d
 
     def take_pending(self):

@@ -52,6 +52,9 @@ class RMSNorm:
         """Fold the pending delta into the residual and return the normed rows."""
         scale = stream.post_scale
         delta, post = stream.take_pending()
+        if post is None and hasattr(delta, "materialize"):
+            # a part's output that is not computed yet and carries no norm of its own
+            delta = ops.convert(delta.materialize(), self.runtime.dtype)
         if post is not None:
             if isinstance(post, RMSNorm):
                 # the sublayer's own norm, the residual sum and this norm as one kernel

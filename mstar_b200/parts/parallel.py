@@ -1,9 +1,19 @@
 """Parallel mixer: several mixers side by side on the same input.  The result is the mean of
 their outputs, each divided by its root mean square over the model width and scaled by a
-weight of its own; the mean is float.  At most one branch may keep keys and values in pages
+weight of its own; the mean is float.  The mixer hands it on uncomputed (``ops.MeanOfNorms``):
+the norm that adds it to the residual does both in one kernel, or computes it first.  At most one branch may keep keys and values in pages
 and at most one a state slot: the layer's cache entry then serves both.
+
+The branches do not depend on one another, so each after the first runs on a stream of its
+own, forked from and joined to the stream of the step (in a captured decode step they become
+parallel branches of the graph): the short kernels of one branch fill the gaps between those
+of the other.  MSTAR_PARALLEL_STREAMS=0 runs them one after the other.
 """
 from __future__ import annotations
+
+import os
+
+import torch
 
 from .. import ops
 from ..weights.names import ParamSpec
@@ -53,10 +63,29 @@ class ParallelMixer:
         self.weights = [params[f"out{b}.weight"].float().contiguous()
                         for b in range(len(spec.branches))]
         self.graph_safe = all(getattr(p, "graph_safe", False) is True for p in self.branches)
+        self.side_streams = None
+        if len(self.branches) > 1 and os.environ.get("MSTAR_PARALLEL_STREAMS") != "0":
+            self.side_streams = [torch.cuda.Stream(device=runtime.device)
+                                 for _ in self.branches[1:]]
 
     def forward(self, x, ctx: StepContext, cache: LayerCache):
-        outs = [branch.forward(x, ctx, cache) for branch in self.branches]
-        return ops.mean_of_norms(outs, self.weights, self.spec.norm_eps)
+        if self.side_streams is None:
+            outs = [branch.forward(x, ctx, cache) for branch in self.branches]
+            return ops.MeanOfNorms(outs, self.weights, self.spec.norm_eps)
+        main = torch.cuda.current_stream(self.runtime.device)
+        outs = [None] * len(self.branches)
+        for b, side in enumerate(self.side_streams, start=1):
+            side.wait_stream(main)                       # x is ready there
+            with torch.cuda.stream(side):
+                outs[b] = self.branches[b].forward(x, ctx, cache)
+        outs[0] = self.branches[0].forward(x, ctx, cache)
+        for side in self.side_streams:
+            main.wait_stream(side)
+        # what the side streams allocated is used on the step's stream from here on
+        for out in outs[1:]:
+            out.record_stream(main)
+        # (left to the norm that adds it to the residual: one kernel for both where it can)
+        return ops.MeanOfNorms(outs, self.weights, self.spec.norm_eps)
 
 
 register_part("mixer", "parallel", ParallelMixer)

@@ -6,7 +6,9 @@ One product gives [x | z]; a kernel runs the causal convolution with SiLU over x
 before a portion's start come from the slot); a second product, with float output, gives
 [dt_in | B | C]; the scan kernel makes the step sizes (softplus(W_dt dt_in + b), float),
 walks each entry's tokens from the state in its slot, gates with silu(z) and moves the
-convolution's window on; the output product follows.  A prompt portion, a decoded token and
+convolution's window on; the output product follows.  Long portions are cut into pieces that
+run side by side (the recurrence is linear in the state, so a piece's effect is its own end
+state plus a decay of whatever came before).  A prompt portion, a decoded token and
 any mix are the same launches.
 """
 from __future__ import annotations
@@ -64,7 +66,7 @@ class SelectiveScan:
         proj = ops.linear(xc, self.w_x, out_dtype=torch.float32, static_weights=True)
         y = ops.selective_scan(xc, xz, proj, self.w_dt, self.dt_bias, self.a_neg, self.d_skip,
                                ctx.qo_indptr, ctx.slots, cache.state, ctx.num_entries, s.inner,
-                               s.state, s.dt_rank, s.conv)
+                               s.state, s.dt_rank, s.conv, max_q_len=ctx.max_q_len)
         return ops.linear(y, self.w_out, static_weights=True)
 
 

@@ -75,6 +75,16 @@ def test_mean_of_normed_branches(dtype):
         got = ops.mean_of_norms([dev(x, dtype) for x in xs], [w.to(DEV) for w in ws], 1e-6)
         assert got.dtype == torch.float32
         close(got, want, "float32", "mean of norms")
+        # left uncomputed, the norm that adds it to the residual takes it along (one kernel
+        # for two branches; computed first otherwise): h += m * norm(mean)
+        h, w = rnd(5, width, seed=30).float(), rnd(width, seed=31, scale=0.5).float()
+        after = h.double().numpy() + 0.3 * P.plain_rms_norm(want, w.double().numpy(), 1e-5)
+        resid = h.clone().to(DEV)
+        pending = ops.MeanOfNorms([dev(x, dtype) for x in xs], [wt.to(DEV) for wt in ws], 1e-6)
+        rows = ops.add_postnorm_rmsnorm(resid, pending, w.to(DEV), 1e-5, 0.0,
+                                        out_dtype=TORCH[dtype], post_scale=0.3, plain_out=True)
+        close(resid, after, "float32", "mean joins the residual")
+        close(rows, after, dtype, "rows after the mean", bf16=5e-3)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -315,6 +325,38 @@ def test_selective_scan_alone(dtype, inner, state, rank, taps):
     close(both[:9], want[:9], dtype, "first of two", bf16=5e-2)
     close(both[9:], want[:30], dtype, "second of two", bf16=5e-2)
     assert float(slots2[1].abs().max()) == 0.0 and float(slots2[3].abs().max()) > 0.0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("inner,state,rank,taps", [(48, 6, 5, 3), (33, 70, 7, 4), (40, 1, 1, 1)])
+def test_selective_scan_long_portions_in_pieces(dtype, inner, state, rank, taps):
+    """A portion long enough to be cut into pieces that run side by side (their end states
+    joined through the decays of the pieces between), beside a short portion of another
+    request in the same batch, then more tokens of both: against the token-by-token
+    recurrence; a piece size that is no divisor of the portion; and the same portion uncut."""
+    from mstar_b200 import ops
+    from mstar_b200.parts import LayerCache
+
+    m = U.right(inner, state, rank, taps)
+    part, spec, p = scan_part(m, 96, dtype, seed=inner)
+    T = ops.SCAN_PIECES_FROM + 2 * ops.SCAN_PIECE + 37
+    x = rnd(T + 20, 96, seed=6)
+    want = P.plain_selective_scan(x.double().numpy(), p, m, {})
+    short = P.plain_selective_scan(x[:9].double().numpy(), p, m, {})
+    size = ops.selective_scan_state_size(inner, state, taps)
+    slots = torch.randn(3, size, device=DEV)
+    slots[:2].zero_()
+    cache = LayerCache(state=slots)
+    got = part.forward(dev(torch.cat([x[:5], x[:T]]), dtype), step_ctx([5, T], [0, 0], [1, 0]), cache)
+    close(got[5:], want[:T], dtype, "pieces", bf16=5e-2)
+    close(got[:5], short[:5], dtype, "short beside pieces", bf16=5e-2)
+    more = part.forward(dev(torch.cat([x[5:9], x[T:]]), dtype), step_ctx([4, 20], [5, T], [1, 0]), cache)
+    close(more[4:], want[T:], dtype, "after pieces", bf16=5e-2)
+    close(more[:4], short[5:], dtype, "short after pieces", bf16=5e-2)
+    slots2 = torch.zeros(1, size, device=DEV)
+    whole = part.forward(dev(x[:ops.SCAN_PIECES_FROM - 1], dtype),
+                         step_ctx([ops.SCAN_PIECES_FROM - 1], [0], [0]), LayerCache(state=slots2))
+    close(whole, want[:ops.SCAN_PIECES_FROM - 1], dtype, "uncut", bf16=5e-2)
 
 
 # ------------------------------------------------------------------ whole models
