@@ -16,17 +16,18 @@ __device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); 
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
 
 // ------------------------------------------------------------------ convolution + SiLU
-// xz: [tokens] rows of ld elements, x in columns [0, inner).  One thread per (token, channel).
+// xz: [tokens] rows of ld elements, x in columns [0, inner).  One thread per (token, channel):
+// a block row of the grid is a token, so neighbours in a warp are neighbouring channels.
 template <typename A, typename W>
 __global__ void conv_silu_kernel(const A* __restrict__ xz, int ld, const W* __restrict__ w,
                                  const W* __restrict__ bias, const int* __restrict__ token_req,
                                  const int* __restrict__ qo_indptr, const int* __restrict__ slots,
                                  const float* __restrict__ state, long long state_stride,
-                                 A* __restrict__ out, int tokens, int inner, int taps) {
+                                 A* __restrict__ out, int t_first, int inner, int taps) {
     xz = pdl_after(xz, pdl_wait());
-    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (size_t)tokens * inner) return;
-    const int t = (int)(idx / inner), c = (int)(idx - (size_t)t * inner);
+    const int t = t_first + blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= inner) return;
+    const size_t idx = (size_t)t * inner + c;
     const int e = token_req[t];
     const int start = qo_indptr[e], local = t - start;
     const float* past = state + (size_t)slots[e] * state_stride;   // [taps-1][inner]
@@ -48,17 +49,19 @@ MSTAR_API int mstar_conv_silu(const void* xz, int ld, const void* w, const void*
     if (tokens <= 0) return 0;
     if (inner <= 0 || taps <= 0) return -1;
     cudaStream_t s = (cudaStream_t)stream;
-    const size_t total = (size_t)tokens * inner;
-    const int threads = 256;
-    const unsigned blocks = (unsigned)((total + threads - 1) / threads);
+    const int threads = inner >= 256 ? 256 : 64;
 #define GO(A, W)                                                                                  \
-    mstar_launch((conv_silu_kernel<A, W>), dim3(blocks), dim3(threads), 0, s, (const A*)xz, ld,   \
+    mstar_launch((conv_silu_kernel<A, W>), blocks, dim3(threads), 0, s, (const A*)xz, ld,         \
                  (const W*)w, (const W*)bias, token_req, qo_indptr, slots, state, state_stride,   \
-                 (A*)out, tokens, inner, taps)
-    if (act_dtype == MSTAR_F32) {
-        if (weight_dtype == MSTAR_F32) { GO(float, float); } else { GO(float, bf16); }
-    } else {
-        if (weight_dtype == MSTAR_F32) { GO(bf16, float); } else { GO(bf16, bf16); }
+                 (A*)out, t0, inner, taps)
+    // (a grid's second dimension ends at 65,535: longer batches go in slices)
+    for (int t0 = 0; t0 < tokens; t0 += 65535) {
+        const dim3 blocks((inner + threads - 1) / threads, tokens - t0 < 65535 ? tokens - t0 : 65535);
+        if (act_dtype == MSTAR_F32) {
+            if (weight_dtype == MSTAR_F32) { GO(float, float); } else { GO(float, bf16); }
+        } else {
+            if (weight_dtype == MSTAR_F32) { GO(bf16, float); } else { GO(bf16, bf16); }
+        }
     }
 #undef GO
     return launch_status();
@@ -88,6 +91,9 @@ struct ScanArgs {
     int piece, pass, max_pieces;
     float* piece_state;   // [entries][max_pieces][inner][n_state]
     float* piece_dt;      // [entries][max_pieces][inner]
+    // W_dt dt_in of every token and channel, made by a product of its own [tokens][inner]
+    // (long portions), or nullptr: the kernel makes it from the staged rows
+    const float* dt_pre;
 };
 
 // A block takes one batch entry and SS_THREADS / LANES channels; LANES lanes share a channel:
@@ -109,7 +115,7 @@ selective_scan_kernel(const A* __restrict__ xc, const A* __restrict__ xz,
     constexpr int CH = SS_THREADS / LANES;
     extern __shared__ float sm[];
     const int row = a.rank + 2 * a.n_state;
-    const int buf_floats = SS_TC * row + 2 * SS_TC * CH;   // rows, then x, then z
+    const int buf_floats = SS_TC * row + 3 * SS_TC * CH;   // rows, then x, z, and W_dt dt_in
     const int e = blockIdx.x;
     const int tid = threadIdx.x, sub = tid % LANES, ch = tid / LANES;
     const int c = blockIdx.y * CH + ch;
@@ -176,7 +182,9 @@ selective_scan_kernel(const A* __restrict__ xc, const A* __restrict__ xz,
     // what a thread fetches of a chunk: its share of the rows, and of the x and z values
     const int row_items = SS_TC * row, xz_items = SS_TC * CH;
     float pf_x[(SS_TC * CH + SS_THREADS - 1) / SS_THREADS],
-        pf_z[(SS_TC * CH + SS_THREADS - 1) / SS_THREADS];
+        pf_z[(SS_TC * CH + SS_THREADS - 1) / SS_THREADS],
+        pf_d[(SS_TC * CH + SS_THREADS - 1) / SS_THREADS];
+    const float* dt_pre = pdl_after(a.dt_pre, waited);
     auto fetch = [&](float* buf, int t0, int nt) {
         const float* src = proj + (size_t)(start + t0) * row;
         for (int i = tid; i < nt * row; i += SS_THREADS) cp_async_4(buf + i, src + i);
@@ -188,6 +196,7 @@ selective_scan_kernel(const A* __restrict__ xc, const A* __restrict__ xz,
             const bool ok = i < xz_items && tk < nt;
             pf_x[k] = ok ? to_float(xc[(size_t)(start + t0 + tk) * a.inner + col]) : 0.f;
             pf_z[k] = ok ? to_float(xz[(size_t)(start + t0 + tk) * a.ld_xz + a.inner + col]) : 0.f;
+            pf_d[k] = (ok && a.dt_pre != nullptr) ? dt_pre[(size_t)(start + t0 + tk) * a.inner + col] : 0.f;
         }
     };
     auto stash = [&](float* buf) {
@@ -198,6 +207,7 @@ selective_scan_kernel(const A* __restrict__ xc, const A* __restrict__ xz,
             if (i < xz_items) {
                 buf[row_items + i] = pf_x[k];
                 buf[row_items + xz_items + i] = pf_z[k];
+                buf[row_items + 2 * xz_items + i] = pf_d[k];
             }
         }
     };
@@ -215,13 +225,18 @@ selective_scan_kernel(const A* __restrict__ xc, const A* __restrict__ xz,
         const float* rows = sm + which * buf_floats;
         const float* xs = rows + row_items;
         const float* zs = xs + xz_items;
+        const float* ds = zs + xz_items;
         if (nt < SS_TC) {
             // a short portion, or a portion's tail: token by token
             for (int k = 0; k < nt; ++k) {
                 float d = 0.f;
-                for (int r = sub; r < a.rank; r += LANES) d = fmaf(wrow[r], rows[k * row + r], d);
+                if (a.dt_pre != nullptr) {
+                    d = ds[k * CH + ch];
+                } else {
+                    for (int r = sub; r < a.rank; r += LANES) d = fmaf(wrow[r], rows[k * row + r], d);
 #pragma unroll
-                for (int o = LANES / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+                    for (int o = LANES / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+                }
                 d = softplus_f(d + bias);
                 dt_sum += d;
                 const float x = xs[k * CH + ch];
@@ -246,17 +261,26 @@ selective_scan_kernel(const A* __restrict__ xc, const A* __restrict__ xz,
         } else {
             // step sizes of the chunk
             float dt[SS_TC];
+            if (a.dt_pre != nullptr) {
 #pragma unroll
-            for (int k = 0; k < SS_TC; ++k) dt[k] = 0.f;
-            for (int r = sub; r < a.rank; r += LANES) {
-                const float w = wrow[r];
+                for (int k = 0; k < SS_TC; ++k) dt[k] = ds[k * CH + ch];
+            } else {
 #pragma unroll
-                for (int k = 0; k < SS_TC; ++k) dt[k] = fmaf(w, rows[k * row + r], dt[k]);
+                for (int k = 0; k < SS_TC; ++k) dt[k] = 0.f;
+                for (int r = sub; r < a.rank; r += LANES) {
+                    const float w = wrow[r];
+#pragma unroll
+                    for (int k = 0; k < SS_TC; ++k) dt[k] = fmaf(w, rows[k * row + r], dt[k]);
+                }
+#pragma unroll
+                for (int k = 0; k < SS_TC; ++k) {
+#pragma unroll
+                    for (int o = LANES / 2; o > 0; o >>= 1)
+                        dt[k] += __shfl_xor_sync(0xffffffffu, dt[k], o);
+                }
             }
 #pragma unroll
             for (int k = 0; k < SS_TC; ++k) {
-#pragma unroll
-                for (int o = LANES / 2; o > 0; o >>= 1) dt[k] += __shfl_xor_sync(0xffffffffu, dt[k], o);
                 dt[k] = softplus_f(dt[k] + bias);
                 dt_sum += dt[k];
             }
@@ -349,25 +373,26 @@ selective_scan_kernel(const A* __restrict__ xc, const A* __restrict__ xz,
 // out [tokens, inner].  piece > 0: portions are cut into pieces of that many tokens (a multiple
 // of the token chunk) that run side by side in two passes; max_pieces bounds the pieces of any
 // entry, piece_state is float scratch [entries, max_pieces, inner, n_state], piece_dt
-// [entries, max_pieces, inner].  Returns 0, a CUDA error code, or -1 when the shape is refused.
+// [entries, max_pieces, inner].  dt_pre: nullptr, or float [tokens, inner] = dt_in W_dt^T made by
+// the caller.  Returns 0, a CUDA error code, or -1 when the shape is refused.
 MSTAR_API int mstar_selective_scan(const void* xc, const void* xz, int ld_xz, const float* proj,
                                    const float* w_dt, const float* dt_bias, const float* a_neg,
                                    const float* d_skip, const int* qo_indptr, const int* slots,
                                    float* state, long long state_stride, void* out, int act_dtype,
                                    int entries, int inner, int n_state, int rank, int taps,
                                    int piece, int max_pieces, float* piece_state, float* piece_dt,
-                                   void* stream) {
+                                   const float* dt_pre, void* stream) {
     if (entries <= 0) return 0;
     if (inner <= 0 || n_state <= 0 || rank <= 0 || taps <= 0 || n_state > 256) return -1;
     if (piece < 0 || (piece > 0 && (max_pieces < 1 || piece_state == nullptr || piece_dt == nullptr)))
         return -1;
     cudaStream_t s = (cudaStream_t)stream;
     ScanArgs a{inner, n_state, rank, taps, ld_xz, entries, state_stride, piece, 0,
-               piece > 0 ? max_pieces : 1, piece_state, piece_dt};
+               piece > 0 ? max_pieces : 1, piece_state, piece_dt, dt_pre};
 #define GO(A, LANES, NPER)                                                                        \
     {                                                                                             \
         constexpr int CH = SS_THREADS / LANES;                                                    \
-        const size_t smem = sizeof(float) * 2 * ((size_t)SS_TC * (rank + 2 * n_state) + 2 * SS_TC * CH); \
+        const size_t smem = sizeof(float) * 2 * ((size_t)SS_TC * (rank + 2 * n_state) + 3 * SS_TC * CH); \
         if (smem > 200 * 1024) return -1;                                                         \
         static size_t configured = 0;                                                             \
         if (smem > 48 * 1024 && smem > configured) {                                              \

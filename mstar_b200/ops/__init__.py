@@ -1147,7 +1147,8 @@ def sink_attention_splits(entries: int, max_q_len: int, num_heads: int, num_kv_h
                           max_keys: int, sms: int | None = None) -> int:
     """Among how many CTAs the keys of a row tile are shared in the tensor-core kernel: one
     where the row tiles alone fill the GPU, else enough for some two CTAs per SM, a split
-    keeping at least two tiles of 64 keys."""
+    keeping at least two tiles of 64 keys (one tile a CTA was measured and is slower: 27
+    against 24 us at 8 requests with 1,028 visible keys)."""
     if sms is None:
         sms = num_sms()
     group = num_heads // num_kv_heads
@@ -1262,7 +1263,7 @@ def selective_scan(xc: torch.Tensor, xz: torch.Tensor, proj: torch.Tensor, w_dt,
     assert state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1
     assert state.shape[1] == selective_scan_state_size(inner, n_state, taps)
     out = torch.empty_like(xc)
-    piece, pieces, piece_state, piece_dt = 0, 1, None, None
+    piece, pieces, piece_state, piece_dt, dt_pre = 0, 1, None, None, None
     if max_q_len is not None and max_q_len >= SCAN_PIECES_FROM:
         piece = int(os.environ.get("MSTAR_SCAN_PIECE", SCAN_PIECE)) // 16 * 16
     if piece:
@@ -1270,11 +1271,15 @@ def selective_scan(xc: torch.Tensor, xz: torch.Tensor, proj: torch.Tensor, w_dt,
         piece_state = torch.empty((entries, pieces, inner, n_state), dtype=torch.float32,
                                   device=xc.device)
         piece_dt = torch.empty((entries, pieces, inner), dtype=torch.float32, device=xc.device)
+        # with many tokens the step sizes' product W_dt dt_in is a true-32-bit product of its
+        # own (a third of the scan's instructions otherwise)
+        dt_pre = sgemm_nt(proj[:, :rank], w_dt)
     code = lib.get("selective_scan").mstar_selective_scan(
         xc.data_ptr(), xz.data_ptr(), xz.stride(0), proj.data_ptr(), w_dt.data_ptr(),
         dt_bias.data_ptr(), a_neg.data_ptr(), d_skip.data_ptr(), qo_indptr.data_ptr(),
         slots.data_ptr(), state.data_ptr(), state.stride(0), out.data_ptr(), _dt(xc), entries,
-        inner, n_state, rank, taps, piece, pieces, _ptr(piece_state), _ptr(piece_dt), _stream())
+        inner, n_state, rank, taps, piece, pieces, _ptr(piece_state), _ptr(piece_dt), _ptr(dt_pre),
+        _stream())
     if piece:
         lib.add_launches(1)                     # two passes behind one call
     if code == -1:

@@ -68,7 +68,7 @@ _SIGNATURES = {
         "mstar_conv_silu": [_vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i,
                             _vp],
         "mstar_selective_scan": [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _vp,
-                                 _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp],
+                                 _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp],
     },
     "attention_generic": {
         "mstar_paged_attention_generic": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i,
