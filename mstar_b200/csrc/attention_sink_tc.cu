@@ -37,7 +37,11 @@ template <int D> __device__ __forceinline__ int st_off(int row, int c) { return 
 
 // NSTAGE key/value tiles are in flight: two where rows are many (the tensor cores set the
 // pace), four where they are few (decoding: the latency of the copies does).
-template <int D, int NSTAGE>
+// KEYSPLIT (an entry's rows fit one warp's 16: decoding): the four warps all take those rows
+// and each a quarter of every key tile (keys 16 w .. 16 w + 15 of the tile), with a running
+// maximum, sum and output of its own; the four are merged through shared memory at the end.
+// One warp alone would issue a tile's products one after the other while three wait.
+template <int D, int NSTAGE, bool KEYSPLIT>
 __global__ void __launch_bounds__(ST_THREADS)
 sink_attention_tc_kernel(SinkTcArgs a) {
     constexpr int CPR = D / 8;
@@ -107,12 +111,13 @@ sink_attention_tc_kernel(SinkTcArgs a) {
     };
 
     // this thread's two rows (g and g+8 of the warp's 16) and their positions
-    const int rowA = row0 + warp * 16 + (lane >> 2), rowB = rowA + 8;
+    const int wrow = KEYSPLIT ? 0 : warp * 16;         // first of the warp's 16 rows in the tile
+    const int rowA = row0 + wrow + (lane >> 2), rowB = rowA + 8;
     const int cpA = past + min(rowA, rows_total - 1) / G;
     const int cpB = past + min(rowB, rows_total - 1) / G;
     // the warp's rows together: newest key any row sees, oldest window key any row sees
-    const int warp_hi = past + min(row0 + warp * 16 + 15, rows_total - 1) / G;
-    const int warp_lo = max(0, past + min(row0 + warp * 16, rows_total - 1) / G - W + 1);
+    const int warp_hi = past + min(row0 + wrow + 15, rows_total - 1) / G;
+    const int warp_lo = max(0, past + min(row0 + wrow, rows_total - 1) / G - W + 1);
 
     float o[D / 8][4];
 #pragma unroll
@@ -142,7 +147,7 @@ sink_attention_tc_kernel(SinkTcArgs a) {
         const int key_first = base < kept ? base : lo + base - kept;
         const int key_last = lo + min(base + ST_TILE, visible) - 1 - kept;
         // (a warp whose rows all lie past the entry's last row has nothing to do)
-        if (row0 + warp * 16 < rows_total &&
+        if (row0 + wrow < rows_total &&
             (base < kept || (key_first <= warp_hi && key_last >= warp_lo))) {
             float s[8][4];
 #pragma unroll
@@ -150,12 +155,12 @@ sink_attention_tc_kernel(SinkTcArgs a) {
 #pragma unroll
             for (int kk = 0; kk < D / 16; ++kk) {
                 uint32_t qa[4];
-                const int arow = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                const int arow = wrow + (lane & 7) + ((lane >> 3) & 1) * 8;
                 ldmatrix_x4(qa, smem_u32(Qs + st_off<D>(arow, 2 * kk + (lane >> 4))));
 #pragma unroll
-                for (int jp = 0; jp < 4; ++jp) {
+                for (int jp = 0; jp < (KEYSPLIT ? 1 : 4); ++jp) {
                     uint32_t kb[4];
-                    const int brow = jp * 16 + (lane & 7) + (lane >> 4) * 8;
+                    const int brow = (KEYSPLIT ? warp : jp) * 16 + (lane & 7) + (lane >> 4) * 8;
                     ldmatrix_x4(kb, smem_u32(Ks + st_off<D>(brow, 2 * kk + ((lane >> 3) & 1))));
                     mma_bf16_16816(s[2 * jp], qa, kb[0], kb[1]);
                     mma_bf16_16816(s[2 * jp + 1], qa, kb[2], kb[3]);
@@ -163,10 +168,10 @@ sink_attention_tc_kernel(SinkTcArgs a) {
             }
             float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
+            for (int j = 0; j < (KEYSPLIT ? 2 : 8); ++j)
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
-                    const int v = base + j * 8 + (lane & 3) * 2 + (q4 & 1);
+                    const int v = base + (KEYSPLIT ? warp * 16 : 0) + j * 8 + (lane & 3) * 2 + (q4 & 1);
                     const int key = v < kept ? v : lo + v - kept;
                     const bool upper = q4 < 2;
                     const int cp = upper ? cpA : cpB;
@@ -186,7 +191,7 @@ sink_attention_tc_kernel(SinkTcArgs a) {
             m1 = mn1;
             float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < (KEYSPLIT ? 2 : 8); ++j) {
                 s[j][0] = exp2f(s[j][0] - b0);
                 s[j][1] = exp2f(s[j][1] - b0);
                 s[j][2] = exp2f(s[j][2] - b1);
@@ -204,7 +209,7 @@ sink_attention_tc_kernel(SinkTcArgs a) {
 #pragma unroll 1
             for (int part = 0; part < 3; ++part) {
 #pragma unroll
-                for (int kk = 0; kk < 4; ++kk) {
+                for (int kk = 0; kk < (KEYSPLIT ? 1 : 4); ++kk) {
                     uint32_t pa[4];
                     pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
                     pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
@@ -220,7 +225,7 @@ sink_attention_tc_kernel(SinkTcArgs a) {
 #pragma unroll
                     for (int n2 = 0; n2 < D / 16; ++n2) {
                         uint32_t vb[4];
-                        const int vrow = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                        const int vrow = (KEYSPLIT ? warp : kk) * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
                         ldmatrix_x4_trans(vb, smem_u32(Vs + st_off<D>(vrow, 2 * n2 + (lane >> 4))));
                         mma_bf16_16816(o[2 * n2], pa, vb[0], vb[1]);
                         mma_bf16_16816(o[2 * n2 + 1], pa, vb[2], vb[3]);
@@ -236,6 +241,52 @@ sink_attention_tc_kernel(SinkTcArgs a) {
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    if constexpr (KEYSPLIT) {
+        // the four warps' partials of rows 0..15 meet in shared memory (the key/value stages are
+        // done with): [warp][row][vd + 2] floats, then every thread sums a share of (row, feature)
+        float* part = reinterpret_cast<float*>(smem_raw);
+        const int pw = a.vd + 2;
+        __syncthreads();
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = (lane >> 2) + 8 * half;
+            float* dst = part + ((size_t)warp * 16 + r) * pw;
+#pragma unroll
+            for (int n = 0; n < D / 8; ++n)
+                if (n * 8 < a.vd) {
+                    dst[n * 8 + (lane & 3) * 2] = o[n][2 * half];
+                    dst[n * 8 + (lane & 3) * 2 + 1] = o[n][2 * half + 1];
+                }
+            if ((lane & 3) == 0) {
+                dst[a.vd] = half ? m1 : m0;
+                dst[a.vd + 1] = half ? l1 : l0;
+            }
+        }
+        __syncthreads();
+        const int rows_here = min(16, rows_total - row0);
+        for (int i = tid; i < rows_here * pw; i += ST_THREADS) {
+            const int r = i / pw, d = i - r * pw;
+            float M = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) M = fmaxf(M, part[((size_t)w * 16 + r) * pw + a.vd]);
+            float L = 0.f, sum = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float* p = part + ((size_t)w * 16 + r) * pw;
+                const float wt = p[a.vd] == -INFINITY ? 0.f : exp2f(p[a.vd] - M);
+                L = fmaf(p[a.vd + 1], wt, L);
+                sum = fmaf(d < a.vd ? p[d] : 0.f, wt, sum);
+            }
+            const int row = row0 + r;
+            const int tok = q_start + row / G, head = kvh * G + row % G;
+            if (a.splits == 1) {
+                if (d < a.vd) a.out[((size_t)tok * a.nq + head) * a.vd + d] = __float2bfloat16_rn(sum / L);
+            } else {
+                float* dst = a.scratch + (((size_t)tok * a.nq + head) * a.splits + split) * pw;
+                dst[d] = d < a.vd ? sum : (d == a.vd ? M : L);
+            }
+        }
+    } else {
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
         const int row = half ? rowB : rowA;
@@ -263,6 +314,7 @@ sink_attention_tc_kernel(SinkTcArgs a) {
                 dst[a.vd + 1] = l;
             }
         }
+    }
     }
 }
 
@@ -300,12 +352,12 @@ __global__ void sink_merge_kernel(const float* __restrict__ scratch, bf16* __res
     }
 }
 
-template <int D, int NSTAGE>
+template <int D, int NSTAGE, bool KEYSPLIT>
 static int launch_sink_tc_stages(const SinkTcArgs& a, int entries, int max_q_len, cudaStream_t s) {
     const size_t smem = (size_t)(2 * NSTAGE + 1) * ST_TILE * (D + 8) * sizeof(bf16);
     static bool configured = false;
     if (!configured && smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(sink_attention_tc_kernel<D, NSTAGE>,
+        cudaError_t e = cudaFuncSetAttribute(sink_attention_tc_kernel<D, NSTAGE, KEYSPLIT>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
@@ -314,18 +366,21 @@ static int launch_sink_tc_stages(const SinkTcArgs& a, int entries, int max_q_len
     const long long tiles = ((long long)max_q_len * G + ST_ROWS - 1) / ST_ROWS;
     if (tiles * a.splits > 2147483647LL) return -1;
     dim3 grid((unsigned)(tiles * a.splits), a.nkv, entries);
-    mstar_launch((sink_attention_tc_kernel<D, NSTAGE>), grid, dim3(ST_THREADS), smem, s, a);
+    mstar_launch((sink_attention_tc_kernel<D, NSTAGE, KEYSPLIT>), grid, dim3(ST_THREADS), smem, s, a);
     return launch_status();
 }
 
 template <int D>
 static int launch_sink_tc(const SinkTcArgs& a, int entries, int max_q_len, cudaStream_t s) {
     // one row tile per (entry, kv head): few rows, deep prefetch (where shared memory has room)
-    const bool few = (long long)max_q_len * (a.nq / a.nkv) <= ST_ROWS;
+    const long long rows = (long long)max_q_len * (a.nq / a.nkv);
     if constexpr (D <= 128) {
-        if (few) return launch_sink_tc_stages<D, 4>(a, entries, max_q_len, s);
+        if (rows <= 16) return launch_sink_tc_stages<D, 4, true>(a, entries, max_q_len, s);
+        if (rows <= ST_ROWS) return launch_sink_tc_stages<D, 4, false>(a, entries, max_q_len, s);
+    } else {
+        if (rows <= 16) return launch_sink_tc_stages<D, 2, true>(a, entries, max_q_len, s);
     }
-    return launch_sink_tc_stages<D, 2>(a, entries, max_q_len, s);
+    return launch_sink_tc_stages<D, 2, false>(a, entries, max_q_len, s);
 }
 
 // Entries [0, entries) of the batch; q: [tokens] rows of q_stride elements; out: [tokens,
