@@ -689,8 +689,10 @@ def vudivik_bench(args) -> int:
         nbytes = 2.0 * entries * size * 4 + tokens * (inner * 3 * 2 + (R + 2 * N) * 4.0)
         record(f"selective_scan_{label}", ms, nbytes=nbytes,
                tokens_per_chain_us=round(per / (ms * 1e3), 3))
+        conv_wt, conv_bf = conv_w.float().t().contiguous(), conv_b.float()
         ms = _time_graph(lambda: ops.conv_silu(xz, conv_w, conv_b, token_req, indptr, slot_sets[0],
-                                               state, inner, taps), reps=8)
+                                               state, inner, taps, weight_t=conv_wt,
+                                               bias_f32=conv_bf), reps=8)
         record(f"conv_silu_{label}", ms, nbytes=tokens * inner * 4.0)
 
     E, ident, top, ff = (moe["router"]["experts"], moe["router"]["identity"], moe["router"]["top"],

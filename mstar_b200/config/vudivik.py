@@ -173,19 +173,13 @@ class VudivikConfig(ModelConfig):
         rd = rd or _Reader()
         norm = NormSpec(kind="rmsnorm", size=self.width, eps=self.norm_eps)
         blocks, owners, block_of, order = [], [], {}, []
+        # first the layers that have tensors, then whose tensors every layer runs: a layer may
+        # name one before or after it, and one that borrows itself passes the name on
         for i, layer in enumerate(self.layers):
             if not isinstance(layer, Mapping):
                 rd.problems.append(f"layers[{i}] must be an object")
                 continue
-            owner = layer.get("weights_of")
-            if owner is not None:
-                # (a layer that itself borrows passes on whose tensors it runs)
-                if isinstance(owner, bool) or not isinstance(owner, int) or owner not in block_of:
-                    rd.problems.append(f"layers[{i}].weights_of must name an earlier layer, "
-                                       f"got {owner!r}")
-                    continue
-                block_of[i] = block_of[owner]
-                order.append(RunEntry(block=block_of[i], cache=i))
+            if layer.get("weights_of") is not None:
                 continue
             mixer = self._mixer(rd, i, layer)
             ffn = self._ffn(rd, i, layer)
@@ -194,7 +188,23 @@ class VudivikConfig(ModelConfig):
             blocks.append(BlockSpec(kind="postnorm", mixer=mixer, ffn=ffn, norm1=None, norm2=None,
                                     norm1_post=norm, norm2_post=None if ffn is None else norm,
                                     residual_mult=self.residual_mult))
-            order.append(RunEntry(block=block_of[i], cache=i))
+        for i, layer in enumerate(self.layers):
+            if not isinstance(layer, Mapping):
+                continue
+            at, seen = i, set()
+            while isinstance(self.layers[at], Mapping) and self.layers[at].get("weights_of") is not None:
+                nxt = self.layers[at]["weights_of"]
+                seen.add(at)
+                if isinstance(nxt, bool) or not isinstance(nxt, int) \
+                        or not 0 <= nxt < len(self.layers) or nxt in seen:
+                    rd.problems.append(f"layers[{i}].weights_of must lead to a layer with tensors "
+                                       f"of its own, got {self.layers[at]['weights_of']!r}")
+                    at = None
+                    break
+                at = nxt
+            if at is None or at not in block_of:
+                continue
+            order.append(RunEntry(block=block_of[at], cache=i))
         return blocks, order, owners
 
     def block_owners(self) -> list:

@@ -41,6 +41,59 @@ __global__ void conv_silu_kernel(const A* __restrict__ xz, int ld, const W* __re
     out[idx] = from_float<A>(silu_f(acc));
 }
 
+// The same for 8 channels a thread with 16-byte accesses: weights transposed to float
+// [taps][inner], bias float; inner and ld multiples of 8.
+template <typename A>
+__global__ void conv_silu_vec_kernel(const A* __restrict__ xz, int ld, const float* __restrict__ wt,
+                                     const float* __restrict__ bias, const int* __restrict__ token_req,
+                                     const int* __restrict__ qo_indptr, const int* __restrict__ slots,
+                                     const float* __restrict__ state, long long state_stride,
+                                     A* __restrict__ out, int t_first, int inner, int taps) {
+    xz = pdl_after(xz, pdl_wait());
+    const int t = t_first + blockIdx.y, c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (c >= inner) return;
+    const int e = token_req[t];
+    const int start = qo_indptr[e], local = t - start;
+    const float* past = state + (size_t)slots[e] * state_stride;
+    float acc[8];
+    load8(bias + c, acc);
+    for (int k = 0; k < taps; ++k) {
+        const int src = local - (taps - 1) + k;
+        float v[8], w[8];
+        if (src >= 0) load8(xz + (size_t)(start + src) * ld + c, v);
+        else load8(past + (size_t)(taps - 1 + src) * inner + c, v);
+        load8(wt + (size_t)k * inner + c, w);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = fmaf(w[i], v[i], acc[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = silu_f(acc[i]);
+    store8(out + (size_t)t * inner + c, acc);
+}
+
+MSTAR_API int mstar_conv_silu_vec(const void* xz, int ld, const float* wt, const float* bias,
+                                  const int* token_req, const int* qo_indptr, const int* slots,
+                                  const float* state, long long state_stride, void* out,
+                                  int act_dtype, int tokens, int inner, int taps, void* stream) {
+    if (tokens <= 0) return 0;
+    if (inner <= 0 || taps <= 0 || inner % 8 || ld % 8 || state_stride % 4) return -1;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int lanes = inner / 8;
+    const int threads = lanes >= 128 ? 128 : 32;
+    for (int t0 = 0; t0 < tokens; t0 += 65535) {
+        const dim3 blocks((lanes + threads - 1) / threads, tokens - t0 < 65535 ? tokens - t0 : 65535);
+        if (act_dtype == MSTAR_F32)
+            mstar_launch((conv_silu_vec_kernel<float>), blocks, dim3(threads), 0, s, (const float*)xz,
+                         ld, wt, bias, token_req, qo_indptr, slots, state, state_stride, (float*)out,
+                         t0, inner, taps);
+        else
+            mstar_launch((conv_silu_vec_kernel<bf16>), blocks, dim3(threads), 0, s, (const bf16*)xz,
+                         ld, wt, bias, token_req, qo_indptr, slots, state, state_stride, (bf16*)out,
+                         t0, inner, taps);
+    }
+    return launch_status();
+}
+
 MSTAR_API int mstar_conv_silu(const void* xz, int ld, const void* w, const void* bias,
                               int weight_dtype, const int* token_req, const int* qo_indptr,
                               const int* slots, const float* state, long long state_stride,
@@ -141,7 +194,8 @@ selective_scan_kernel(const A* __restrict__ xc, const A* __restrict__ xz,
     for (int i = 0; i < NPER; ++i) {
         const int n = sub + LANES * i;
         S[i] = 0.f;
-        An[i] = n < a.n_state ? a_neg[(size_t)cc * a.n_state + n] : 0.f;
+        // A in units of log2(e): the decays are then 2^(dt A), one exponential instruction
+        An[i] = n < a.n_state ? a_neg[(size_t)cc * a.n_state + n] * 1.4426950408889634f : 0.f;
     }
     // The state the portion starts from.  Cut into pieces, the last piece puts the new state
     // into the slot while others may not have started: so pass 1 leaves a copy of the old one
@@ -171,7 +225,7 @@ selective_scan_kernel(const A* __restrict__ xc, const A* __restrict__ xz,
 #pragma unroll
             for (int i = 0; i < NPER; ++i) {
                 const int n = sub + LANES * i;
-                if (n < a.n_state) S[i] = fmaf(expf(sdt * An[i]), S[i], E[n]);
+                if (n < a.n_state) S[i] = fmaf(exp2f(sdt * An[i]), S[i], E[n]);
             }
         }
     }
@@ -248,7 +302,7 @@ selective_scan_kernel(const A* __restrict__ xc, const A* __restrict__ xz,
                 for (int i = 0; i < NPER; ++i) {
                     const int n = sub + LANES * i;
                     if (n < a.n_state) {
-                        S[i] = fmaf(expf(d * An[i]), S[i], dx * B[n]);
+                        S[i] = fmaf(exp2f(d * An[i]), S[i], dx * B[n]);
                         y = fmaf(S[i], C[n], y);
                     }
                 }
@@ -301,7 +355,7 @@ selective_scan_kernel(const A* __restrict__ xc, const A* __restrict__ xz,
                     for (int i = 0; i < NPER; ++i) {
                         const int n = sub + LANES * i;
                         const bool use = n < a.n_state;
-                        da[kk][i] = use ? expf(dt[k] * An[i]) : 1.f;
+                        da[kk][i] = use ? exp2f(dt[k] * An[i]) : 1.f;
                         db[kk][i] = use ? dx * B[use ? n : 0] : 0.f;
                     }
                 }

@@ -1215,17 +1215,31 @@ def selective_scan_state_size(inner: int, n_state: int, taps: int) -> int:
 
 
 def conv_silu(xz: torch.Tensor, weight, bias, token_req, qo_indptr, slots, state: torch.Tensor,
-              inner: int, taps: int) -> torch.Tensor:
+              inner: int, taps: int, weight_t=None, bias_f32=None) -> torch.Tensor:
     """silu(causal convolution per channel) of the x half of ``xz`` [tokens, 2 * inner], the
     inputs before a portion's start taken from the request's slot.  ``weight`` [inner, taps]
-    (last column: the current token), ``bias`` [inner]."""
-    _need_cuda(xz, weight, bias, token_req, qo_indptr, slots, state)
+    (last column: the current token), ``bias`` [inner].  With ``weight_t`` (float [taps,
+    inner]) and ``bias_f32`` given and rows of whole 16-byte pieces, a thread takes 8 channels
+    with 16-byte accesses."""
+    _need_cuda(xz, weight, bias, token_req, qo_indptr, slots, state, weight_t, bias_f32)
     assert xz.dim() == 2 and xz.stride(1) == 1 and weight.is_contiguous() and bias.is_contiguous()
     assert tuple(weight.shape) == (inner, taps) and bias.numel() == inner
     assert weight.dtype == bias.dtype
     assert state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1
     tokens = xz.shape[0]
     out = torch.empty((tokens, inner), dtype=xz.dtype, device=xz.device)
+    if (weight_t is not None and bias_f32 is not None and inner % 8 == 0 and xz.stride(0) % 8 == 0
+            and state.stride(0) % 4 == 0 and xz.data_ptr() % 16 == 0
+            and os.environ.get("MSTAR_CONV") != "scalar"):
+        assert weight_t.dtype == torch.float32 and tuple(weight_t.shape) == (taps, inner)
+        assert bias_f32.dtype == torch.float32 and bias_f32.numel() == inner
+        assert weight_t.is_contiguous() and bias_f32.is_contiguous()
+        check(lib.get("selective_scan").mstar_conv_silu_vec(
+            xz.data_ptr(), xz.stride(0), weight_t.data_ptr(), bias_f32.data_ptr(),
+            token_req.data_ptr(), qo_indptr.data_ptr(), slots.data_ptr(), state.data_ptr(),
+            state.stride(0), out.data_ptr(), _dt(xz), tokens, inner, taps, _stream()),
+            "conv_silu_vec")
+        return out
     check(lib.get("selective_scan").mstar_conv_silu(
         xz.data_ptr(), xz.stride(0), weight.data_ptr(), bias.data_ptr(), _dt(weight),
         token_req.data_ptr(), qo_indptr.data_ptr(), slots.data_ptr(), state.data_ptr(),

@@ -67,6 +67,7 @@ _SIGNATURES = {
     "selective_scan": {
         "mstar_conv_silu": [_vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i,
                             _vp],
+        "mstar_conv_silu_vec": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i, _vp],
         "mstar_selective_scan": [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _vp,
                                  _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp],
     },

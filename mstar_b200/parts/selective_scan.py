@@ -52,6 +52,9 @@ class SelectiveScan:
         self.w_out = params["o.weight"]
         self.conv_w = params["conv.weight"].contiguous()
         self.conv_b = params["conv.bias"].to(self.conv_w.dtype).contiguous()
+        # for the kernel that takes 8 channels a thread: taps-major float weights
+        self.conv_wt = self.conv_w.float().t().contiguous()
+        self.conv_bf = self.conv_b.float().contiguous()
         # everything that enters the recurrence beside x, B and C is float
         self.w_dt = params["dt.weight"].float().contiguous()
         self.dt_bias = params["dt.bias"].float().contiguous()
@@ -62,7 +65,8 @@ class SelectiveScan:
         s = self.spec
         xz = ops.linear(x, self.w_in, static_weights=True)
         xc = ops.conv_silu(xz, self.conv_w, self.conv_b, ctx.token_req, ctx.qo_indptr, ctx.slots,
-                           cache.state, s.inner, s.conv)
+                           cache.state, s.inner, s.conv, weight_t=self.conv_wt,
+                           bias_f32=self.conv_bf)
         proj = ops.linear(xc, self.w_x, out_dtype=torch.float32, static_weights=True)
         y = ops.selective_scan(xc, xz, proj, self.w_dt, self.dt_bias, self.a_neg, self.d_skip,
                                ctx.qo_indptr, ctx.slots, cache.state, ctx.num_entries, s.inner,

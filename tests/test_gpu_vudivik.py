@@ -195,7 +195,11 @@ def paged_cache(part_spec, tokens, page, dtype, seed=1):
                          [(4, 2, 24, 40, 11, 3, 16, 4), (3, 3, 16, 8, 9, 0, 16, 8),
                           (6, 2, 20, 20, 5, 18, None, 16), (2, 1, 32, 48, None, 0, 8, 4),
                           (2, 2, 64, 64, 1, 1, 64, 8), (8, 1, 16, 16, 16, 16, 2, 16),
-                          (5, 5, 96, 96, 33, 6, 96, 16)])
+                          (5, 5, 96, 96, 33, 6, 96, 16),
+                          # the two widest compiled sizes; 34 query heads on one kv head (more
+                          # rows than a warp's 16 in decoding, more than a tile's 64 in prompts)
+                          (4, 2, 128, 128, 20, 3, 64, 16), (2, 1, 160, 256, 7, 2, 32, 8),
+                          (34, 1, 16, 24, 12, 2, 8, 4)])
 def test_window_attention_alone(dtype, heads, kv_heads, dim, vdim, size, keep, rot, page):
     """The attention branch alone with scores so sharp that a query's weight lies on a few
     keys: a key that a window one too long or too short, or one kept key too many or too few,
@@ -471,12 +475,17 @@ def test_long_decoding_past_many_windows(dtype):
 def test_sizes_that_are_one_or_equal(dtype):
     """One query head on one key head, a value as wide as a key, a window of one, a kept first
     key alone, a state of one, one tap, one expert of which one is chosen, a multiplier of
-    one; and a second model whose layers all share the first layer's tensors."""
+    one; a second model whose layers all share the first layer's tensors; and one whose first
+    layer runs the second's."""
     for layers, mult in (([U.layer(U.left(1, 1, 16, 16, size=1, keep_first=1, rot_dims=16, scale=0.25),
                                    U.right(16, 1, 1, 1), U.moe(1, 0, 1, 8))], 1.0),
                          ([U.layer(U.left(2, 2, 8, 8, size=3, keep_first=2, rot_dims=4, scale=0.5),
                                    U.right(8, 2, 2, 2), U.dense(16)),
-                           U.layer(weights_of=0), U.layer(weights_of=1)], 0.7)):
+                           U.layer(weights_of=0), U.layer(weights_of=1)], 0.7),
+                         # a layer that runs the tensors of the layer after it
+                         ([U.layer(weights_of=1),
+                           U.layer(U.left(2, 1, 8, 16, size=4, keep_first=1, rot_dims=8, scale=0.5),
+                                   U.right(16, 3, 2, 3), U.moe(2, 1, 2, 8))], 0.5)):
         cfg = U.config(layers, width=32, vocab=50, mult=mult)
         weights = U.random_weights(cfg, 21)
         reqs = {"x": U.tokens(cfg, 33, 1), "y": U.tokens(cfg, 12, 2)}

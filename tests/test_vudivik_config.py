@@ -56,6 +56,26 @@ def test_layout_reads_every_size_and_constant_per_layer():
     assert windows == [(11, 3), 21, (5, 18), None] and group_of == [0, 1, 0, 2, 1, 3, 0]
 
 
+def test_a_layer_may_borrow_from_a_later_one_and_through_another():
+    raw = U.config([U.layer(weights_of=2), U.layer(weights_of=0), U.layer(mlp=U.dense(16)),
+                    U.layer(U.left(size=None), mlp=None)], width=32, vocab=50)
+    raw["layers"][0] = dict(raw["layers"][2], weights_of=2)
+    raw["layers"][1] = dict(raw["layers"][2], weights_of=0)
+    cfg = config_from_dict(raw)
+    lay = cfg.layout()
+    assert [(e.block, e.cache) for e in lay.order] == [(0, 0), (0, 1), (0, 2), (1, 3)]
+    assert cfg.block_owners() == [2, 3]
+    names = {s.name.split(".")[0] for s in get_architecture("Vudivik").checkpoint_map(cfg, lay).sources}
+    assert names == {"embed", "final", "head", "l2", "l3"}
+    # the plain implementation follows the same chain
+    w = U.as_numpy(U.random_weights(raw, 5))
+    assert set(k.split(".")[0] for k in w) == names
+    assert P.plain_forward(U.tokens(raw, 6, 1), w, raw).shape == (6, 50)
+    raw["layers"][2] = dict(raw["layers"][2], weights_of=0)        # a circle
+    with pytest.raises(ConfigError, match="weights_of"):
+        config_from_dict(raw)
+
+
 def test_checkpoint_names_cover_the_parameters():
     cfg = config_from_dict(U.MIXED)
     lay = cfg.layout()
@@ -78,7 +98,7 @@ def test_missing_and_unusable_keys_are_named_together():
     del raw["layers"][0]["mixer"]["left"]["scale"]
     raw["layers"][1]["mixer"]["right"]["conv"] = 0
     raw["layers"][3]["type"] = "serial"
-    raw["layers"][4]["weights_of"] = 9
+    raw["layers"][4]["weights_of"] = 19
     with pytest.raises(ConfigError) as err:
         config_from_dict(raw)
     text = str(err.value)
