@@ -205,16 +205,18 @@ sink_attention_tc_kernel(SinkTcArgs a) {
             for (int n = 0; n < D / 8; ++n) {
                 o[n][0] *= al0; o[n][1] *= al0; o[n][2] *= al1; o[n][3] *= al1;
             }
-            // O += P V with P = P1 + P2 + P3, three bfloat16 parts that hold the float exactly
-#pragma unroll 1
-            for (int part = 0; part < 3; ++part) {
+            // O += P V with P = P1 + P2 + P3, three bfloat16 parts that hold the float exactly.
+            // A block of 16 keys at a time: its three parts of P, then every value fragment
+            // is fetched once and meets all three.
 #pragma unroll
-                for (int kk = 0; kk < (KEYSPLIT ? 1 : 4); ++kk) {
-                    uint32_t pa[4];
-                    pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-                    pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-                    pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-                    pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+            for (int kk = 0; kk < (KEYSPLIT ? 1 : 4); ++kk) {
+                uint32_t pa[3][4];
+#pragma unroll
+                for (int part = 0; part < 3; ++part) {
+                    pa[part][0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+                    pa[part][1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+                    pa[part][2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+                    pa[part][3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
                     if (part < 2) {            // what the parts so far leave
 #pragma unroll
                         for (int jj = 0; jj < 2; ++jj)
@@ -222,13 +224,19 @@ sink_attention_tc_kernel(SinkTcArgs a) {
                             for (int q4 = 0; q4 < 4; ++q4)
                                 s[2 * kk + jj][q4] -= __bfloat162float(__float2bfloat16_rn(s[2 * kk + jj][q4]));
                     }
+                }
+                const int vrow = (KEYSPLIT ? warp : kk) * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
 #pragma unroll
-                    for (int n2 = 0; n2 < D / 16; ++n2) {
-                        uint32_t vb[4];
-                        const int vrow = (KEYSPLIT ? warp : kk) * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-                        ldmatrix_x4_trans(vb, smem_u32(Vs + st_off<D>(vrow, 2 * n2 + (lane >> 4))));
-                        mma_bf16_16816(o[2 * n2], pa, vb[0], vb[1]);
-                        mma_bf16_16816(o[2 * n2 + 1], pa, vb[2], vb[3]);
+                for (int n2 = 0; n2 < D / 16; n2 += 2) {
+                    uint32_t vb[2][4];
+                    ldmatrix_x4_trans(vb[0], smem_u32(Vs + st_off<D>(vrow, 2 * n2 + (lane >> 4))));
+                    ldmatrix_x4_trans(vb[1], smem_u32(Vs + st_off<D>(vrow, 2 * n2 + 2 + (lane >> 4))));
+#pragma unroll
+                    for (int part = 0; part < 3; ++part) {
+                        mma_bf16_16816(o[2 * n2], pa[part], vb[0][0], vb[0][1]);
+                        mma_bf16_16816(o[2 * n2 + 1], pa[part], vb[0][2], vb[0][3]);
+                        mma_bf16_16816(o[2 * n2 + 2], pa[part], vb[1][0], vb[1][1]);
+                        mma_bf16_16816(o[2 * n2 + 3], pa[part], vb[1][2], vb[1][3]);
                     }
                 }
             }

@@ -316,8 +316,20 @@ selective_scan_kernel(const A* __restrict__ xc, const A* __restrict__ xz,
             // step sizes of the chunk
             float dt[SS_TC];
             if (a.dt_pre != nullptr) {
+                // the softplus of a channel's 16 step sizes is dealt out among its lanes (in
+                // place in the staged values), not made by each of them
+                float* dsw = sm + which * buf_floats + row_items + 2 * xz_items;
 #pragma unroll
-                for (int k = 0; k < SS_TC; ++k) dt[k] = ds[k * CH + ch];
+                for (int j = 0; j < SS_TC / LANES; ++j) {
+                    const int k = sub + LANES * j;
+                    dsw[k * CH + ch] = softplus_f(dsw[k * CH + ch] + bias);
+                }
+                __syncwarp();
+#pragma unroll
+                for (int k = 0; k < SS_TC; ++k) {
+                    dt[k] = ds[k * CH + ch];
+                    dt_sum += dt[k];
+                }
             } else {
 #pragma unroll
                 for (int k = 0; k < SS_TC; ++k) dt[k] = 0.f;
@@ -332,11 +344,11 @@ selective_scan_kernel(const A* __restrict__ xc, const A* __restrict__ xz,
                     for (int o = LANES / 2; o > 0; o >>= 1)
                         dt[k] += __shfl_xor_sync(0xffffffffu, dt[k], o);
                 }
-            }
 #pragma unroll
-            for (int k = 0; k < SS_TC; ++k) {
-                dt[k] = softplus_f(dt[k] + bias);
-                dt_sum += dt[k];
+                for (int k = 0; k < SS_TC; ++k) {
+                    dt[k] = softplus_f(dt[k] + bias);
+                    dt_sum += dt[k];
+                }
             }
             // the chain, SUB tokens at a time: first everything that does not depend on the
             // state (decays exp(dt A), inputs dt x B), then one multiply-add per state and token
