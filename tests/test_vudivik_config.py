@@ -187,3 +187,25 @@ def test_kept_first_pages_stay_with_the_request():
     cm.reserve(["a"], [20])
     cm.commit("a", 20)
     assert cm.block_table("a")[:3] == [-1, -1, -1]
+
+
+def test_command_line_writes_a_random_model_of_this_design(tmp_path, capsys):
+    """``mstar random-model`` with a Vudivik configuration: the folder holds the design's
+    tensor names (none for a layer that borrows), and its configuration reads back."""
+    import json
+
+    from safetensors import safe_open
+
+    from mstar_b200.cli import main as cli
+    from mstar_b200.config.registry import load_config
+
+    src = tmp_path / "config.json"
+    src.write_text(json.dumps(U.MIXED))
+    out = tmp_path / "model"
+    cli.main(["random-model", str(src), str(out), "--seed", "5", "--std", "0.05"])
+    assert str(out) in capsys.readouterr().out
+    assert load_config(out).to_dict() == config_from_dict(U.MIXED).to_dict()
+    with safe_open(str(out / "model.safetensors"), framework="pt") as f:
+        assert set(f.keys()) == set(U.random_weights(U.MIXED, 1))
+        assert tuple(f.get_tensor("l0.mix.right.A_log").shape) == (48, 6)
+        assert tuple(f.get_tensor("l1.mlp.correction").shape) == (7,)
