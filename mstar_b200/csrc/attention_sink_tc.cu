@@ -226,17 +226,22 @@ sink_attention_tc_kernel(SinkTcArgs a) {
                     }
                 }
                 const int vrow = (KEYSPLIT ? warp : kk) * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                // NG value fragments at a time: 2 NG sums lie between two products into the
+                // same one
+                constexpr int NG = (D / 16) % 4 == 0 ? 4 : 2;
 #pragma unroll
-                for (int n2 = 0; n2 < D / 16; n2 += 2) {
-                    uint32_t vb[2][4];
-                    ldmatrix_x4_trans(vb[0], smem_u32(Vs + st_off<D>(vrow, 2 * n2 + (lane >> 4))));
-                    ldmatrix_x4_trans(vb[1], smem_u32(Vs + st_off<D>(vrow, 2 * n2 + 2 + (lane >> 4))));
+                for (int n2 = 0; n2 < D / 16; n2 += NG) {
+                    uint32_t vb[NG][4];
+#pragma unroll
+                    for (int q = 0; q < NG; ++q)
+                        ldmatrix_x4_trans(vb[q], smem_u32(Vs + st_off<D>(vrow, 2 * (n2 + q) + (lane >> 4))));
 #pragma unroll
                     for (int part = 0; part < 3; ++part) {
-                        mma_bf16_16816(o[2 * n2], pa[part], vb[0][0], vb[0][1]);
-                        mma_bf16_16816(o[2 * n2 + 1], pa[part], vb[0][2], vb[0][3]);
-                        mma_bf16_16816(o[2 * n2 + 2], pa[part], vb[1][0], vb[1][1]);
-                        mma_bf16_16816(o[2 * n2 + 3], pa[part], vb[1][2], vb[1][3]);
+#pragma unroll
+                        for (int q = 0; q < NG; ++q) {
+                            mma_bf16_16816(o[2 * (n2 + q)], pa[part], vb[q][0], vb[q][1]);
+                            mma_bf16_16816(o[2 * (n2 + q) + 1], pa[part], vb[q][2], vb[q][3]);
+                        }
                     }
                 }
             }
