@@ -78,6 +78,9 @@ struct SbRope {
     const float* inv_freq;   // [hd / 2]
     bf16* kv_cache;          // [pages, 2, nkv, page_size, hd]
     int nq, nkv, hd, page_size, bt_stride;
+    // plain form only: 1 squares the positive part of every sum before it is stored (a
+    // feed-forward's first product with its relu-squared, as one kernel)
+    int act;
 };
 
 __host__ __device__ constexpr int sb_rows(bool gated, int nt) { return (gated ? 16 : 8) * nt; }
@@ -299,6 +302,11 @@ smallm_bulk_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT*
                     continue;
                 }
                 float y = v[0];
+                if (MODE == SB_PLAIN && rp.act == 1) {
+                    // rounded to bfloat16 first, as the unfused path stores the product
+                    const float r = fmaxf(__bfloat162float(__float2bfloat16_rn(y)), 0.f);
+                    y = r * r;
+                }
                 if (MODE == SB_GATED) {
                     // gate and up are rounded to bfloat16 first, as the unfused path stores them
                     const float gate = __bfloat162float(__float2bfloat16_rn(v[0]));
@@ -361,13 +369,15 @@ static int pick_nt(int n_out, bool gated, bool m16) {
 
 template <bool GATED, bool M16, typename OutT>
 static int launch_bulk(const bf16* x, const bf16* W, OutT* out, int M, int n_out, int K, int ldx, int ldw,
-                       int ldo, int inter, int w_static, int* error_word, cudaStream_t s) {
+                       int ldo, int inter, int w_static, int* error_word, cudaStream_t s, int act = 0) {
+    SbRope rp{};
+    rp.act = act;
     switch (pick_nt(n_out, GATED, M16)) {
         case 4:
             if constexpr (!GATED)
-                return launch_bulk_nt<GATED ? SB_GATED : SB_PLAIN, M16, 4, OutT>(x, W, out, M, n_out, K, ldx, ldw, ldo, inter, w_static, error_word, s);
-        case 2: return launch_bulk_nt<GATED ? SB_GATED : SB_PLAIN, M16, 2, OutT>(x, W, out, M, n_out, K, ldx, ldw, ldo, inter, w_static, error_word, s);
-        default: return launch_bulk_nt<GATED ? SB_GATED : SB_PLAIN, M16, 1, OutT>(x, W, out, M, n_out, K, ldx, ldw, ldo, inter, w_static, error_word, s);
+                return launch_bulk_nt<GATED ? SB_GATED : SB_PLAIN, M16, 4, OutT>(x, W, out, M, n_out, K, ldx, ldw, ldo, inter, w_static, error_word, s, rp);
+        case 2: return launch_bulk_nt<GATED ? SB_GATED : SB_PLAIN, M16, 2, OutT>(x, W, out, M, n_out, K, ldx, ldw, ldo, inter, w_static, error_word, s, rp);
+        default: return launch_bulk_nt<GATED ? SB_GATED : SB_PLAIN, M16, 1, OutT>(x, W, out, M, n_out, K, ldx, ldw, ldo, inter, w_static, error_word, s, rp);
     }
 }
 
@@ -400,6 +410,22 @@ MSTAR_API int mstar_gemm_smallm_bulk_bf16(const void* x, const void* W, void* ou
     }
     if (M > 8) return launch_bulk<false, true, bf16>(xp, wp, (bf16*)out, M, N, K, ldx, ldw, ldo, 0, w_static, error_word, s);
     return launch_bulk<false, false, bf16>(xp, wp, (bf16*)out, M, N, K, ldx, ldw, ldo, 0, w_static, error_word, s);
+}
+
+// out[M, N] = relu(x W^T)^2 in bfloat16: the plain product with the activation of a feed-forward
+// without a gate where the sums are made.  Arguments and refusals as above.
+MSTAR_API int mstar_gemm_smallm_bulk_relu2_bf16(const void* x, const void* W, void* out, int M, int N,
+                                                int K, int ldx, int ldw, int ldo, int w_static,
+                                                int* error_word, void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > 16 || K <= 0 || K % 32 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || error_word == nullptr) return -1;
+    if (((uintptr_t)x & 15) != 0 || ((uintptr_t)W & 15) != 0) return -1;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (M > 8)
+        return launch_bulk<false, true, bf16>((const bf16*)x, (const bf16*)W, (bf16*)out, M, N, K, ldx, ldw,
+                                              ldo, 0, w_static, error_word, s, 1);
+    return launch_bulk<false, false, bf16>((const bf16*)x, (const bf16*)W, (bf16*)out, M, N, K, ldx, ldw,
+                                           ldo, 0, w_static, error_word, s, 1);
 }
 
 // The attention mixer's first product for few tokens, with the rotary encoding and the cache

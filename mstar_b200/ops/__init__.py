@@ -643,6 +643,25 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
     return convert(y, out_dtype)
 
 
+def linear_act(x: torch.Tensor, w: torch.Tensor, kind: str, static_weights: bool = False):
+    """act(x W^T) for a feed-forward without a gate (``kind``: see ``ACTIVATIONS``): one kernel
+    for few bfloat16 rows and the square of relu (MSTAR_FUSED_ACT=0: never), else the product
+    followed by the activation kernel."""
+    _need_cuda(x, w)
+    if (kind == "relu2" and _smallm_ok(x, w) and os.environ.get("MSTAR_FUSED_ACT") != "0"):
+        m, k = x.shape
+        n = w.shape[0]
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+        code = lib.get("gemm_smallm_bulk").mstar_gemm_smallm_bulk_relu2_bf16(
+            x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, x.stride(0), w.stride(0),
+            out.stride(0), int(static_weights), tcgen05_error_word(x.device).data_ptr(), _stream())
+        if code == -1:
+            raise KernelError(f"small-M GEMM refuses M={m}, N={n}, K={k}")
+        check(code, "gemm_smallm_bulk_relu2")
+        return out
+    return activation(linear(x, w, static_weights=static_weights), kind)
+
+
 def gated_up(x: torch.Tensor, w_gate_up: torch.Tensor, static_weights: bool = False):
     """silu(x Wg^T) * (x Wu^T) for the fused matrix [Wg; Wu]: one kernel for few
     bfloat16 rows, else the product followed by the SiLU-multiply kernel."""

@@ -33,7 +33,8 @@ class GatedMLP:
 
 class MLP:
     """down(act(up(x))) without a gate; the activation (relu squared, tanh gelu or silu) is
-    a kernel of its own between the two products."""
+    a kernel of its own between the two products, or, for a few rows and relu squared, the
+    epilogue of the first."""
 
     graph_safe = True
 
@@ -54,7 +55,7 @@ class MLP:
         self.down = params["down.weight"]
 
     def forward(self, x, ctx):
-        h = ops.activation(ops.linear(x, self.up, static_weights=True), self.spec.activation)
+        h = ops.linear_act(x, self.up, self.spec.activation, static_weights=True)
         return ops.linear(h, self.down, static_weights=True)
 
 

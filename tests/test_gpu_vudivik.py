@@ -93,12 +93,20 @@ def test_feed_forward_without_a_gate(dtype):
     from mstar_b200.config.layout import MLPSpec
     from mstar_b200.parts import build_part
 
-    x = rnd(9, 72, seed=6)
-    up, down = rnd(200, 72, seed=4, scale=0.1), rnd(72, 200, seed=5, scale=0.1)
-    part = build_part("ffn", MLPSpec(hidden_size=72, intermediate_size=200),
-                      {"up.weight": dev(up, dtype), "down.weight": dev(down, dtype)}, runtime(dtype))
-    want = P.plain_relu2_mlp(x.double().numpy(), up.double().numpy(), down.double().numpy())
-    close(part.forward(dev(x, dtype), None), want, dtype, "relu squared", bf16=2e-2)
+    # a few rows (in bfloat16 the activation is the epilogue of the first product) and many;
+    # a width of whole 64-byte pieces (that kernel's) and one that is not
+    for rows, width in ((9, 96), (40, 96), (9, 72)):
+        x = rnd(rows, width, seed=6)
+        up, down = rnd(200, width, seed=4, scale=0.1), rnd(width, 200, seed=5, scale=0.1)
+        part = build_part("ffn", MLPSpec(hidden_size=width, intermediate_size=200),
+                          {"up.weight": dev(up, dtype), "down.weight": dev(down, dtype)},
+                          runtime(dtype))
+        want = P.plain_relu2_mlp(x.double().numpy(), up.double().numpy(), down.double().numpy())
+        close(part.forward(dev(x, dtype), None), want, dtype, ("relu squared", rows, width), bf16=2e-2)
+    if dtype == "bfloat16":
+        h = ops.linear_act(dev(x, dtype)[:, :64].contiguous(), dev(up, dtype)[:, :64].contiguous(), "relu2")
+        ref = torch.relu(x[:, :64].double() @ up[:, :64].double().T) ** 2
+        close(h, ref, dtype, "fused up product", bf16=2e-2)
     z = rnd(3, 50, seed=7, scale=2.0).double()
     gelu = 0.5 * z * (1 + torch.tanh((2 / torch.pi) ** 0.5 * (z + 0.044715 * z ** 3)))
     close(ops.activation(dev(z, dtype), "gelu_tanh", inplace=False), gelu, dtype, "gelu", bf16=1e-2)
