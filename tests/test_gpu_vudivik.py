@@ -483,18 +483,24 @@ def test_long_decoding_past_many_windows(dtype):
 def test_sizes_that_are_one_or_equal(dtype):
     """One query head on one key head, a value as wide as a key, a window of one, a kept first
     key alone, a state of one, one tap, one expert of which one is chosen, a multiplier of
-    one; a second model whose layers all share the first layer's tensors; and one whose first
-    layer runs the second's."""
-    for layers, mult in (([U.layer(U.left(1, 1, 16, 16, size=1, keep_first=1, rot_dims=16, scale=0.25),
-                                   U.right(16, 1, 1, 1), U.moe(1, 0, 1, 8))], 1.0),
-                         ([U.layer(U.left(2, 2, 8, 8, size=3, keep_first=2, rot_dims=4, scale=0.5),
-                                   U.right(8, 2, 2, 2), U.dense(16)),
-                           U.layer(weights_of=0), U.layer(weights_of=1)], 0.7),
-                         # a layer that runs the tensors of the layer after it
-                         ([U.layer(weights_of=1),
-                           U.layer(U.left(2, 1, 8, 16, size=4, keep_first=1, rot_dims=8, scale=0.5),
-                                   U.right(16, 3, 2, 3), U.moe(2, 1, 2, 8))], 0.5)):
-        cfg = U.config(layers, width=32, vocab=50, mult=mult)
+    one; a second model whose layers all share the first layer's tensors; one whose first
+    layer runs the second's; and one whose sizes are multiples of nothing (a width of 100,
+    heads of 12 and 10, 50 channels, a vocabulary of 53)."""
+    for layers, mult, width, vocab in (
+            ([U.layer(U.left(1, 1, 16, 16, size=1, keep_first=1, rot_dims=16, scale=0.25),
+                      U.right(16, 1, 1, 1), U.moe(1, 0, 1, 8))], 1.0, 32, 50),
+            ([U.layer(U.left(2, 2, 8, 8, size=3, keep_first=2, rot_dims=4, scale=0.5),
+                      U.right(8, 2, 2, 2), U.dense(16)),
+              U.layer(weights_of=0), U.layer(weights_of=1)], 0.7, 32, 50),
+            # a layer that runs the tensors of the layer after it
+            ([U.layer(weights_of=1),
+              U.layer(U.left(2, 1, 8, 16, size=4, keep_first=1, rot_dims=8, scale=0.5),
+                      U.right(16, 3, 2, 3), U.moe(2, 1, 2, 8))], 0.5, 32, 50),
+            ([U.layer(U.left(3, 1, 12, 10, size=6, keep_first=2, rot_dims=6, scale=0.4),
+                      U.right(50, 5, 3, 3), U.dense(36)),
+              U.layer(U.left(3, 3, 12, 10, size=9, keep_first=0, rot_dims=12, scale=0.4),
+                      U.right(50, 5, 3, 2), U.moe(3, 1, 2, 20))], 0.6, 100, 53)):
+        cfg = U.config(layers, width=width, vocab=vocab, mult=mult)
         weights = U.random_weights(cfg, 21)
         reqs = {"x": U.tokens(cfg, 33, 1), "y": U.tokens(cfg, 12, 2)}
         want = {r: U.plain_logits(cfg, weights, t) for r, t in reqs.items()}
