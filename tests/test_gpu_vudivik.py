@@ -51,7 +51,7 @@ def test_normed_output_joins_the_residual_with_a_multiplier(dtype):
     float (the mixer's mean of norms) and in the compute dtype (a feed-forward's output)."""
     from mstar_b200 import ops
 
-    for width, m in ((64, 0.3), (200, 1.0), (1000, 2.5)):
+    for width, m in ((64, 0.35), (200, 1.0), (1000, 2.5)):
         h, w = rnd(7, width, seed=1).float(), rnd(width, seed=3, scale=0.5).float()
         for y in (rnd(7, width, seed=2, scale=3.0).float(), dev(rnd(7, width, seed=2, scale=3.0), dtype)):
             want = h.double().numpy() + m * P.plain_rms_norm(y.double().cpu().numpy(), w.double().numpy(), 1e-5)
@@ -203,7 +203,7 @@ def paged_cache(part_spec, tokens, page, dtype, seed=1):
                          [(4, 2, 24, 40, 11, 3, 16, 4), (3, 3, 16, 8, 9, 0, 16, 8),
                           (6, 2, 20, 20, 5, 18, None, 16), (2, 1, 32, 48, None, 0, 8, 4),
                           (2, 2, 64, 64, 1, 1, 64, 8), (8, 1, 16, 16, 16, 16, 2, 16),
-                          (5, 5, 96, 96, 33, 6, 96, 16),
+                          (5, 5, 96, 96, 33, 7, 96, 16),
                           # the two widest compiled sizes; 34 query heads on one kv head (more
                           # rows than a warp's 16 in decoding, more than a tile's 64 in prompts)
                           (4, 2, 128, 128, 20, 3, 64, 16), (2, 1, 160, 256, 7, 2, 32, 8),
